@@ -1,0 +1,72 @@
+"""ctypes binding of libgact_b200.so (declared in include/gact_b200.h).
+
+The library is required: importing this module without it raises, and nothing in the package falls back to
+a CPU or pure-PyTorch implementation of the kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libgact_b200.so"
+
+F32, F16, BF16 = 0, 1, 2
+DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+RNG_CURAND, RNG_FAST, RNG_RTN, RNG_EXTERNAL = 0, 1, 2, 3
+RNG_CODE = {"curand": RNG_CURAND, "fast": RNG_FAST, "rtn": RNG_RTN, "external": RNG_EXTERNAL}
+GROUP = 256
+
+if not LIB_PATH.exists():
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python gact-icml_b200/build.py` "
+        "(nvcc, sm_100a).  gact has no fallback path.")
+
+lib = C.CDLL(str(LIB_PATH))
+
+_vp, _i, _i64, _u64, _d = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_double
+_SIGNATURES = {
+    "gact_version": ([], _i),
+    "gact_error_string": ([_i], C.c_char_p),
+    "gact_packed_bytes": ([_i64, _i], _i64),
+    "gact_quantize": ([_vp, _i, _i64, _i, _u64, _i, _vp, _i, _vp, _vp, _vp, _vp], _i),
+    "gact_dequantize": ([_vp, _vp, _vp, _i, _i64, _i, _vp, _vp], _i),
+    "gact_minimax": ([_vp, _i, _i64, _vp, _vp, _vp], _i),
+    "gact_mask_words": ([_i64], _i64),
+    "gact_mask_pack": ([_vp, _i64, _vp, _vp, _vp], _i),
+    "gact_mask_unpack": ([_vp, _i64, _vp, _vp], _i),
+    "gact_sq_diffs3_scratch_bytes": ([], _i64),
+    "gact_sq_diffs3": ([_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _vp, _vp], _i),
+    "gact_sensitivity": ([_vp, _d, _vp, _i, _vp], _i),
+    "gact_calc_precision": ([_vp, _vp, _vp, _i, _d, _vp, _vp], _i),
+}
+for _name, (_args, _res) in _SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = _res
+
+
+class GactError(RuntimeError):
+    pass
+
+
+def check(status: int, what: str) -> None:
+    """Raise like the reference's TORCH_CHECK does (RuntimeError) on a non-zero status; argument errors
+    become ValueError."""
+    if status == 0:
+        return
+    msg = f"{what}: {lib.gact_error_string(status).decode()} (status {status})"
+    if status in (1, 2, 5, 6):
+        raise ValueError(msg)
+    raise GactError(msg)
+
+
+def require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor!")       # same wording as the reference's check
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream

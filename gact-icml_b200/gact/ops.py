@@ -1,0 +1,144 @@
+"""The op contract of the compression path (reference: gact/gact/ops.py:11-69).
+
+``op_quantize(input, q_bit, seed) -> [q_input, q_bit, q_scale, q_min]`` and
+``op_dequantize([q_input, q_bit, q_scale, q_min], shape) -> Tensor`` keep the reference's return shapes
+and dtypes: ``q_input`` is a 1-D int8 tensor of R*256 + 1 bytes (the reference allocates one spare byte),
+``q_scale`` / ``q_min`` have shape (G, 1, 1) in the input dtype.  Unlike the reference there is no padding
+copy, no separate min/max pass and no scale kernel: one fused kernel reads the tensor once.
+"""
+import numpy as np
+import torch
+
+from gact.conf import config
+from gact import _native as nv
+
+
+def _numel(shape):
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
+
+
+def quantize_pack(input, q_bit, seed, rng_mode=None, noise=None, fma=None):
+    """Fused minimax + scale + stochastic rounding + packing.  Returns (q_input, q_scale, q_min)."""
+    nv.require_cuda(input, "input")
+    if input.dtype not in nv.DTYPE_CODE:
+        raise RuntimeError("The type of input is not correct!")
+    x = input if input.is_contiguous() else input.contiguous()
+    n = x.numel()
+    G = (n + nv.GROUP - 1) // nv.GROUP
+    nbytes = nv.lib.gact_packed_bytes(n, q_bit)
+    if nbytes < 0:
+        raise ValueError("bits must be 1, 2, 4, 8 or 32, got %r" % (q_bit,))
+    q_input = torch.empty(nbytes + 1, dtype=torch.int8, device=x.device)
+    # bf16 (not a reference type) keeps its scale in fp32; q_min always carries the tensor's dtype
+    q_scale = torch.empty((G, 1, 1), dtype=torch.float32 if x.dtype == torch.bfloat16 else x.dtype, device=x.device)
+    q_min = torch.empty((G, 1, 1), dtype=x.dtype, device=x.device)
+    mode = nv.RNG_CODE[rng_mode if rng_mode is not None else config.rng_mode]
+    noise_ptr = None
+    if mode == nv.RNG_EXTERNAL:
+        noise = noise.to(device=x.device, dtype=torch.float32).contiguous()
+        if noise.numel() != G * nv.GROUP:
+            raise ValueError("noise must have G*256 elements")
+        noise_ptr = noise.data_ptr()
+    with torch.cuda.device(x.device):
+        st = nv.lib.gact_quantize(x.data_ptr(), nv.DTYPE_CODE[x.dtype], n, q_bit, int(seed) & 0xFFFFFFFFFFFFFFFF, mode,
+                                  noise_ptr, int(config.fma if fma is None else fma), q_input.data_ptr(),
+                                  q_min.data_ptr(), q_scale.data_ptr(), nv.stream_ptr())
+    nv.check(st, "gact_quantize")
+    return q_input, q_scale, q_min
+
+
+def no_scheme_quantize_pack(input, q_bit, seed):
+    """Reference: gact/gact/ops.py:11-32."""
+    if q_bit == 32:
+        # uncompressed passthrough used by the debug path: the payload is the zero-padded (G, 256) view
+        nv.require_cuda(input, "input")
+        n = input.numel()
+        G = (n + config.group_size - 1) // config.group_size
+        if G * config.group_size != n:
+            flat = input.new_zeros(G * config.group_size)
+            flat[:n] = input.reshape(-1)
+        else:
+            flat = input.reshape(-1)
+        groups = flat.reshape(G, config.group_size)
+        q_min = groups.min(dim=-1, keepdim=True).values
+        q_scale = groups.max(dim=-1, keepdim=True).values - q_min
+        return groups, q_scale, q_min
+    return quantize_pack(input, q_bit, seed)
+
+
+def dequantize_and_unpack(data, shape, q_bit, scale, mn):
+    """Reference: gact/gact/ops.py:34-47.  Returns the tensor already in ``shape`` (n elements, no padding)."""
+    if not isinstance(q_bit, int):
+        print("bits must be intergers, now bits ", q_bit)
+        assert False
+    if q_bit == 32:
+        return data
+    nv.require_cuda(data, "data")
+    n = _numel(shape)
+    out = torch.empty(tuple(int(s) for s in shape), dtype=mn.dtype, device=data.device)
+    with torch.cuda.device(data.device):
+        st = nv.lib.gact_dequantize(data.data_ptr(), mn.data_ptr(), scale.data_ptr(), nv.DTYPE_CODE[mn.dtype], n, q_bit,
+                                    out.data_ptr(), nv.stream_ptr())
+    nv.check(st, "gact_dequantize")
+    return out
+
+
+def op_quantize_mask(input, flag=None):
+    """1 bit per element for a 0/1 uint8 (or bool) tensor; returns [int32 words, shape]
+    (reference: gact/gact/ops.py:49-50).  ``flag``: optional int32 device scalar, pre-zeroed, set to 1 by the
+    kernel when some element is neither 0 nor 1."""
+    nv.require_cuda(input, "input")
+    if input.dtype not in (torch.uint8, torch.bool):
+        raise RuntimeError("The type of data is not correct!")
+    x = input.contiguous()
+    n = x.numel()
+    words = torch.empty(nv.lib.gact_mask_words(n), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = nv.lib.gact_mask_pack(x.data_ptr(), n, words.data_ptr(), None if flag is None else flag.data_ptr(),
+                                   nv.stream_ptr())
+    nv.check(st, "gact_mask_pack")
+    return [words, input.shape]
+
+
+def op_dequantize_mask(input, dtype=torch.uint8):
+    """Reference: gact/gact/ops.py:52-55."""
+    q_mask, input_shape = input
+    n = _numel(input_shape)
+    out = torch.empty(tuple(int(s) for s in input_shape), dtype=torch.uint8, device=q_mask.device)
+    with torch.cuda.device(q_mask.device):
+        st = nv.lib.gact_mask_unpack(q_mask.data_ptr(), n, out.data_ptr(), nv.stream_ptr())
+    nv.check(st, "gact_mask_unpack")
+    return out if dtype == torch.uint8 else out.view(dtype)
+
+
+def op_quantize(input, q_bit, seed):
+    """Reference: gact/gact/ops.py:57-59."""
+    q_input, q_scale, q_min = no_scheme_quantize_pack(input, q_bit, seed)
+    return [q_input, q_bit, q_scale, q_min]
+
+
+def op_dequantize(input, input_shape):
+    """Reference: gact/gact/ops.py:61-69."""
+    q_input, q_bit, q_scale, q_min = input
+    out = dequantize_and_unpack(q_input, input_shape, q_bit, q_scale, q_min)
+    if q_bit == 32:
+        num_features = int(np.prod(input_shape))
+        out = out.ravel()[:num_features].reshape(*input_shape).contiguous()
+    return out
+
+
+def minimax(data):
+    """Per-row min and max of a (N, 256) tensor (reference binding: gact/gact/cpp_extension/minimax.cc:7-14)."""
+    nv.require_cuda(data, "data")
+    if data.dim() != 2 or data.shape[1] != nv.GROUP:
+        raise RuntimeError("minimax expects rows of 256 elements")
+    x = data.contiguous()
+    mn = torch.empty(x.shape[0], dtype=x.dtype, device=x.device)
+    mx = torch.empty_like(mn)
+    with torch.cuda.device(x.device):
+        st = nv.lib.gact_minimax(x.data_ptr(), nv.DTYPE_CODE[x.dtype], x.numel(), mn.data_ptr(), mx.data_ptr(), nv.stream_ptr())
+    nv.check(st, "gact_minimax")
+    return mn, mx

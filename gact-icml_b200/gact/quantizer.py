@@ -1,0 +1,196 @@
+"""Per-step bookkeeping of the saved-tensor compression (reference: gact/gact/quantizer.py).
+
+Decides which saved tensors are compressed, numbers them in forward order (``tid``), looks up their bit
+width and seed, and keeps the compressed payloads in a ref-counted map until backward asks for them.
+The tuples handed to autograd keep the reference's formats:
+``(False, tensor)`` | ``(True, True, [mask_words, shape])`` | ``(True, False, key, shape, tid)``.
+"""
+import torch
+
+from gact.conf import config
+from gact.ops import op_quantize, op_dequantize, op_quantize_mask, op_dequantize_mask
+from gact.utils import uniform_sample
+
+
+class Quantizer:
+    """
+    default_bit: bits per element until auto precision decides otherwise
+    swap: move compressed payloads to pinned host memory after the forward pass
+    prefetch: while tensor ``tid`` is dequantized, bring tensor ``tid - 1`` back on a side stream
+              (only meaningful with swap)
+    """
+
+    def __init__(self, default_bit, swap, prefetch):
+        self.unrelated_tensors = set()      # data_ptr of tensors never to be compressed (parameters)
+        self.default_bit = default_bit
+        self.swap = swap
+        if swap:
+            self.swap_out_stream = torch.cuda.Stream()
+            self.swap_in_stream = torch.cuda.Stream()
+        self.compute_stream = torch.cuda.current_stream() if torch.cuda.is_available() else None
+        self.ptr_qtensor_map = {}
+        self.prefetch = prefetch
+        if prefetch:
+            self.start_prefetch_event = torch.cuda.Event(blocking=True)
+            self.end_prefetch_event = torch.cuda.Event(blocking=True)
+        self.layer_key_map = {}
+        self.tid = 0
+        self.start_bwd = True
+        # collected for auto precision
+        self.seeds = {}
+        self.bits = {}
+        self.dims = {}
+        self.iter = 0        # iterations seen, the extra probe passes of auto precision included
+        self.seed_iter = 0   # seed component shared by all passes of one optimizer step
+        # added to every seed so that data-parallel ranks draw independent noise (0 on a single process)
+        self.seed_offset = 0
+        self._mask_flag = None
+
+    def filter_tensors(self, pairs):
+        for _, v in pairs:
+            self.unrelated_tensors.add(v.data_ptr())
+
+    # returns (should_be_quantized, is_dropout_mask)
+    def check_quantize(self, input_tensor):
+        # parameters are not compressed
+        if input_tensor.data_ptr() in self.unrelated_tensors:
+            return False, False
+        # 0/1 byte tensors (dropout masks) take the 1-bit path
+        if input_tensor.numel() > 0:
+            if input_tensor.dtype == torch.bool and config.pack_bool_masks:
+                return input_tensor.is_cuda, True
+            if input_tensor.dtype == torch.uint8:
+                # decided after packing, from the flag the pack kernel raises (see quantize)
+                return input_tensor.is_cuda, True
+        dtypes = (torch.float32, torch.float16, torch.bfloat16) if config.quantize_bf16 \
+            else (torch.float32, torch.float16)
+        if input_tensor.dtype not in dtypes:
+            return False, False
+        # only activations that take part in the gradient (e.g. not BN running statistics)
+        if input_tensor.requires_grad is False:
+            return False, False
+        # 2-D, 3-D and 4-D tensors only, as in the reference
+        if input_tensor.dim() not in (2, 3, 4):
+            return False, False
+        if not input_tensor.is_cuda:
+            return False, False
+        return True, False
+
+    def __del__(self):
+        self.ptr_qtensor_map = None
+        self.layer_key_map = None
+        self.unrelated_tensors = None
+
+    def iterate(self):
+        self.ptr_qtensor_map = {}
+        self.layer_key_map = {}
+        self.tid = 0
+        self.start_bwd = True
+        self.iter += 1
+
+    def generate_tensor_key(self, t, tid):
+        if config.check_dup:
+            # 100 evenly spaced values + the data pointer + the sum of the tensor
+            sample_cnt = min(100, t.numel())
+            key = uniform_sample(t, sample_cnt, add_dataptr=True)
+            key.append(t.sum().item())
+            return tuple(key)
+        return tid
+
+    def _quantize_mask(self, input):
+        if input.dtype == torch.bool:
+            return True, True, op_quantize_mask(input) + [torch.bool]
+        # uint8: the reference compresses only tensors whose max is 1 and min is 0, found with two
+        # synchronising reductions; here the pack kernel reports non-binary content through a flag and the
+        # tensor is kept as it is in that case.  One small read-back instead of two reductions.
+        if self._mask_flag is None or self._mask_flag.device != input.device:
+            self._mask_flag = torch.zeros(1, dtype=torch.int32, device=input.device)
+        q_inputs = op_quantize_mask(input, flag=self._mask_flag)
+        if int(self._mask_flag.item()) != 0:
+            self._mask_flag.zero_()
+            return False, input
+        return True, True, q_inputs
+
+    def quantize(self, input):
+        quantize, is_dropout_mask = self.check_quantize(input)
+        if not quantize:
+            return False, input
+        if is_dropout_mask:
+            return self._quantize_mask(input)
+
+        tid = self.tid
+        self.tid += 1
+        input_shape = input.shape
+
+        key = self.generate_tensor_key(input, tid)
+        self.layer_key_map[tid] = key
+        entry = self.ptr_qtensor_map.get(key)
+        if entry is None:
+            if self.iter == 0:
+                bit = self.default_bit
+                self.bits[tid] = bit
+                self.dims[tid] = input.numel()
+                self.seeds[tid] = tid
+            else:
+                bit = self.bits[tid]
+            q_inputs = op_quantize(input, bit, self.seeds[tid] + self.seed_iter + self.seed_offset)
+            if self.swap:
+                self._swap_out(q_inputs)
+            self.ptr_qtensor_map[key] = [q_inputs, 1, tid]
+        else:
+            entry[1] += 1       # same tensor saved again: share the payload
+        return True, is_dropout_mask, key, input_shape, tid
+
+    def _swap_out(self, q_inputs):
+        # device -> pinned host copy of the packed bytes on the side stream, ordered after the kernel that
+        # produced them; the device buffer is handed back to the allocator once the copy has been queued.
+        q_gpu = q_inputs[0]
+        self.swap_out_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.swap_out_stream):
+            q_cpu = torch.empty(q_gpu.shape, dtype=q_gpu.dtype, device="cpu", pin_memory=True)
+            q_cpu.copy_(q_gpu, non_blocking=True)
+        q_gpu.record_stream(self.swap_out_stream)
+        q_inputs[0] = q_cpu
+
+    def dequantize(self, input):
+        quantized = input[0]
+        if not quantized:
+            return input[1]
+        is_dropout_mask = input[1]
+        if is_dropout_mask:
+            q_inputs = input[2]
+            if len(q_inputs) == 3:
+                return op_dequantize_mask(q_inputs[:2], dtype=q_inputs[2])
+            return op_dequantize_mask(q_inputs)
+
+        _, _, key, input_shape, tid = input
+        q_inputs, ref_cnt, key_tid = self.ptr_qtensor_map[key]
+
+        if self.swap:
+            cur = torch.cuda.current_stream()
+            if self.start_bwd:
+                cur.wait_stream(self.swap_out_stream)      # all swap-outs of the forward pass have landed
+                self.start_bwd = False
+            if self.prefetch:
+                cur.wait_stream(self.swap_in_stream)       # a prefetch of this tensor may be in flight
+            if not q_inputs[0].is_cuda:
+                q_inputs[0] = q_inputs[0].cuda(non_blocking=True)
+            if self.prefetch and tid > 0:
+                previous_key = self.layer_key_map.get(tid - 1)
+                prev = self.ptr_qtensor_map.get(previous_key) if previous_key is not None else None
+                if prev is not None and not prev[0][0].is_cuda:
+                    self.swap_in_stream.wait_stream(cur)
+                    with torch.cuda.stream(self.swap_in_stream):
+                        prev[0][0] = prev[0][0].cuda(non_blocking=True)
+                    prev[0][0].record_stream(cur)
+
+        ret = op_dequantize(q_inputs, input_shape)
+
+        ref_cnt -= 1
+        if ref_cnt < 0:
+            raise RuntimeError("[Error] Ref count < 0 %s %d" % (str(key), ref_cnt))
+        elif ref_cnt == 0:
+            del self.ptr_qtensor_map[key]
+        else:
+            self.ptr_qtensor_map[key] = [q_inputs, ref_cnt, key_tid]
+        return ret

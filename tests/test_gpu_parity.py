@@ -1,0 +1,155 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle on the same inputs.
+
+Bar: packed codes, per-group min and scale, and dequantized values are bit-exact (integer / IEEE work on
+both sides; NaN payloads are normalised before comparing).
+"""
+import pytest
+import torch
+
+import oracle
+from helpers import abi_dequantize, abi_quantize, assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+BITS = [1, 2, 4, 8]
+# sizes: single element, around one group, ragged (n % 256 != 0), G % wpt != 0 for every width, several tiles
+SIZES = [1, 255, 256, 257, 7700, 256 * 13, 256 * 64 + 5, 100 * 77]
+
+
+def make_input(kind, n, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, generator=g)
+    if kind == "relu":
+        x = x.clamp_min(0)
+    elif kind == "uniform":
+        x = torch.rand(n, generator=g)
+    elif kind == "large":
+        x = x * 3.0e4
+    elif kind == "tiny":
+        x = x * 1e-6
+    elif kind == "const":
+        x = torch.full((n,), 1.25)
+    elif kind == "special":
+        x = x.clone()
+        idx = torch.randperm(n, generator=g)
+        k = max(1, n // 50)
+        x[idx[:k]] = float("nan")
+        x[idx[k:2 * k]] = float("inf")
+        x[idx[2 * k:3 * k]] = float("-inf")
+        x[idx[3 * k:6 * k]] = 0.0
+        x[idx[6 * k:9 * k]] = -0.0
+    elif kind == "zeros_signed":
+        # groups whose extreme is a zero of either sign: the reported sign follows the reference's order
+        x = x.abs()
+        idx = torch.randperm(n, generator=g)
+        x[idx[: n // 3]] = 0.0
+        x[idx[n // 3: n // 2]] = -0.0
+        if n > 600:
+            x[256:512] = -x[256:512]          # a group that is all <= 0 with zeros at the top
+            x[512:600] = 0.0
+            x[600:768] = -0.0                  # a group of zeros of both signs only
+    return x.to(dtype)
+
+
+def check_case(x_cpu, bits, seed, rng_mode, fma=True, noise=None):
+    x = x_cpu.cuda()
+    pk, mn, sc = abi_quantize(x, bits, seed, rng_mode, noise=noise, fma=fma)
+    opk, omn, osc = oracle.quantize(x_cpu, bits, seed, rng_mode, noise=noise, fma=fma)
+    tag = f"{x_cpu.dtype} b={bits} n={x_cpu.numel()} {rng_mode}"
+    assert_bits_equal(mn, omn, "qmin " + tag)
+    assert_bits_equal(sc, osc, "qscale " + tag)
+    assert_bits_equal(pk, opk, "packed " + tag)
+    out = abi_dequantize(pk, mn, sc, x_cpu.numel(), bits)
+    oout = oracle.dequantize(opk, omn, osc, x_cpu.numel(), bits)
+    assert_bits_equal(out, oout, "dequantized " + tag)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bits", BITS)
+def test_quantize_sizes(dtype, bits):
+    for n in SIZES:
+        check_case(make_input("randn", n, dtype, seed=n), bits, seed=n % 7, rng_mode="curand")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bits", BITS)
+@pytest.mark.parametrize("kind", ["relu", "uniform", "large", "tiny", "const", "special", "zeros_signed"])
+def test_quantize_distributions(dtype, bits, kind):
+    if kind == "large" and dtype == torch.float16:
+        pass  # overflows to inf in fp16: still a valid (and interesting) input
+    check_case(make_input(kind, 256 * 37 + 19, dtype, seed=3), bits, seed=11, rng_mode="curand")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bits", BITS)
+def test_round_to_nearest_and_external_noise(dtype, bits):
+    n = 256 * 21 + 100
+    x = make_input("randn", n, dtype, seed=5)
+    check_case(x, bits, 0, "rtn")
+    G = (n + 255) // 256
+    g = torch.Generator().manual_seed(9)
+    noise = torch.rand(G * 256, generator=g)
+    noise[::97] = 1.0          # the value that can push a code past 2^bits - 1 (no upper clamp)
+    noise[5::89] = 0.0
+    check_case(x, bits, 0, "external", noise=noise)
+
+
+@pytest.mark.parametrize("bits", BITS)
+def test_fp32_unfused_multiply_add(bits):
+    x = make_input("randn", 256 * 40 + 3, torch.float32, seed=8)
+    check_case(x, bits, 4, "curand", fma=False)
+    check_case(x, bits, 4, "rtn", fma=False)
+
+
+def test_seed_is_64_bit():
+    x = make_input("randn", 256 * 9, torch.float32, seed=1)
+    for seed in (0, 1, 2**32 - 1, 2**32, (5 << 32) + 17, 2**64 - 1):
+        check_case(x, 2, seed, "curand")
+
+
+def test_config1_single_tensor_round_trip():
+    """fp32 32x128x768 from N(0,1) with seed 0, group 256, 2 bit, seed 0."""
+    torch.manual_seed(0)
+    x = torch.randn(32, 128, 768)
+    check_case(x.reshape(-1), 2, 0, "curand")
+
+
+def test_many_row_blocks_grid_stride():
+    """More tiles than the launch has warps, so every warp loops."""
+    x = make_input("relu", 256 * 40000 + 77, torch.float16, seed=2)
+    check_case(x, 8, 3, "curand")
+    check_case(x, 1, 3, "curand")
+
+
+def test_minimax_entry_point():
+    from gact import _native as nv
+    for dtype in DTYPES:
+        x_cpu = make_input("zeros_signed", 256 * 33 + 10, dtype, seed=4)
+        x = x_cpu.cuda()
+        G = (x.numel() + 255) // 256
+        mn = torch.empty(G, dtype=dtype, device="cuda")
+        mx = torch.empty(G, dtype=dtype, device="cuda")
+        st = nv.lib.gact_minimax(x.data_ptr(), nv.DTYPE_CODE[dtype], x.numel(), mn.data_ptr(), mx.data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        omn, omx = oracle.minimax(x_cpu)
+        assert_bits_equal(mn, omn, "min")
+        assert_bits_equal(mx, omx, "max")
+
+
+def test_argument_errors():
+    from gact import _native as nv
+    x = torch.zeros(512, device="cuda")
+    pk = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    q = torch.zeros(8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    f = nv.lib.gact_quantize
+    assert f(x.data_ptr(), 0, 512, 3, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 1      # bits
+    assert f(x.data_ptr(), 7, 512, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 2      # dtype
+    assert f(None, 0, 512, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 3              # null
+    assert f(x.data_ptr() + 4, 0, 500, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 4  # alignment
+    assert f(x.data_ptr(), 0, -1, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 5       # size
+    assert f(x.data_ptr(), 0, 512, 2, 0, 3, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 6      # noise missing
+    assert f(x.data_ptr(), 0, 0, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 0        # empty input
+    torch.cuda.synchronize()
