@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""Benchmark of the activation-compression hot path (quantize + dequantize GB/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--rng curand|fast|rtn]
+
+Workload (the kernel sweep the metric is quoted on): post-ReLU activations of shape
+128x64x112x112 in fp16 and bf16 at 1/2/4/8 bits, plus a mixed list of 50 fp16 tensors of 2^20..2^26 elements with
+widths drawn from {2,4,8}.  One step = a "forward" phase that quantizes every tensor of the set followed by a
+"backward" phase that dequantizes them in reverse order, so that nothing a kernel reads is still in L2 from the
+kernel that wrote it (the set moves ~10 GB per step; every big tensor is larger than L2).
+`value` = algorithmic bytes (read + written) of all launches of all ranks / max-over-ranks device
+time, inputs resident in HBM.  `e2e` = the same bytes through the public ops (gact.ops.op_quantize /
+op_dequantize) starting from pinned host buffers and ending with the reconstructed tensors back in host memory.
+
+`--impl reference` times the CPU restatement of the reference quantizer (the oracle; the reference has no CPU
+implementation of its own) on the host cores over a bounded sample of the same workload.
+
+One process per GPU under torchrun for N > 1: every rank compresses its own tensors, no collective on the data
+path (weak scaling).  Rank 0 prints exactly one JSON line on stdout.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT, ROOT / "gact-icml_b200"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+import torch  # noqa: E402
+
+GROUP = 256
+METRIC = "act quant+dequant GB/s"
+BIG_SHAPE = (128, 64, 112, 112)
+
+
+def alg_bytes(n: int, bits: int, elem_size: int, scale_size: int) -> int:
+    """Algorithmic bytes of ONE direction (quantize, or dequantize): the tensor, the packed codes, min + scale."""
+    G = (n + GROUP - 1) // GROUP
+    wpt = 8 // bits
+    R = (G + wpt - 1) // wpt
+    return n * elem_size + R * GROUP + G * (elem_size + scale_size)
+
+
+def workload_spec():
+    """[(name, dtype, numel, bits)] of the sweep.  Mixed list: numel = 2^k, k ~ U{20..26} (seed 1), bits ~ U{2,4,8}
+    (seed 2)."""
+    spec = []
+    n_big = 1
+    for s in BIG_SHAPE:
+        n_big *= s
+    for dt in (torch.float16, torch.bfloat16):
+        for bits in (1, 2, 4, 8):
+            spec.append((f"relu_{str(dt).split('.')[-1]}_b{bits}", dt, n_big, bits))
+    g1 = torch.Generator().manual_seed(1)
+    g2 = torch.Generator().manual_seed(2)
+    ks = torch.randint(20, 27, (50,), generator=g1).tolist()
+    bs = [(2, 4, 8)[i] for i in torch.randint(0, 3, (50,), generator=g2).tolist()]
+    for i, (k, b) in enumerate(zip(ks, bs)):
+        spec.append((f"mixed{i:02d}_2^{k}_b{b}", torch.float16, 1 << k, b))
+    return spec
+
+
+def spec_bytes(spec):
+    total = 0
+    for _, dt, n, bits in spec:
+        es = 2 if dt != torch.float32 else 4
+        ss = 4 if dt == torch.bfloat16 else es
+        total += 2 * alg_bytes(n, bits, es, ss)
+    return total
+
+
+# ----------------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, smax, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); smax.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def make_inputs(spec, device, seed):
+    """Synthetic stand-ins with the sweep's shapes and value distributions: N(0,1) clamped at 0 (about half exact
+    zeros) for the big tensors, N(0,1) for the mixed list.  Tensors that share dtype and size share storage."""
+    cache = {}
+    g = torch.Generator(device=device).manual_seed(seed)
+    xs = []
+    for name, dt, n, bits in spec:
+        key = (dt, n, name.startswith("relu"))
+        if key not in cache:
+            x = torch.randn(n, device=device, generator=g)
+            if name.startswith("relu"):
+                x = x.clamp_min_(0)
+            cache[key] = x.to(dt)
+        xs.append(cache[key])
+    return xs
+
+
+def run_ours(args):
+    import gact
+    from gact import _native as nv
+    from gact.ops import op_quantize, op_dequantize
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    spec = workload_spec()
+    xs = make_inputs(spec, dev, seed=1234 + rank)
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+    mode = nv.RNG_CODE[args.rng]
+
+    # ---- device-resident arm: straight through the C ABI, outputs preallocated -------------------------------
+    bufs = []
+    for (name, dt, n, bits), x in zip(spec, xs):
+        G = (n + GROUP - 1) // GROUP
+        nb = nv.lib.gact_packed_bytes(n, bits)
+        sdt = torch.float32 if dt == torch.bfloat16 else dt
+        bufs.append((torch.empty(nb, dtype=torch.uint8, device=dev), torch.empty(G, dtype=dt, device=dev),
+                     torch.empty(G, dtype=sdt, device=dev)))
+    out_big = {}
+    for (name, dt, n, bits) in spec:
+        if (dt, n) not in out_big:
+            out_big[(dt, n)] = torch.empty(n, dtype=dt, device=dev)
+
+    def forward_phase(step):
+        for i, ((name, dt, n, bits), x) in enumerate(zip(spec, xs)):
+            pk, mn, sc = bufs[i]
+            st = nv.lib.gact_quantize(x.data_ptr(), nv.DTYPE_CODE[dt], n, bits, i + step, mode, None, 1, pk.data_ptr(),
+                                      mn.data_ptr(), sc.data_ptr(), sp)
+            if st:
+                raise RuntimeError(nv.lib.gact_error_string(st).decode())
+
+    def backward_phase():
+        for i in range(len(spec) - 1, -1, -1):
+            name, dt, n, bits = spec[i]
+            pk, mn, sc = bufs[i]
+            st = nv.lib.gact_dequantize(pk.data_ptr(), mn.data_ptr(), sc.data_ptr(), nv.DTYPE_CODE[dt], n, bits,
+                                        out_big[(dt, n)].data_ptr(), sp)
+            if st:
+                raise RuntimeError(nv.lib.gact_error_string(st).decode())
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for w in range(args.warmup):
+        forward_phase(w); backward_phase()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    ev[0].record(stream)
+    for k in range(args.steps):
+        forward_phase(args.warmup + k)
+        ev[2 * k + 1].record(stream)
+        backward_phase()
+        ev[2 * k + 2].record(stream)
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    q_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps))
+    d_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(args.steps))
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- per-kernel table on rank 0 (stderr): every case timed alone with an L2 flush between launches ------
+    table = {}
+    if rank == 0 and not args.no_table:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        for i, (name, dt, n, bits) in enumerate(spec[:8]):
+            es = 2
+            by = alg_bytes(n, bits, es, 4 if dt == torch.bfloat16 else 2)
+            pk, mn, sc = bufs[i]
+            tq, td = [], []
+            for rep in range(7):
+                flush.zero_()
+                a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                a.record(stream)
+                nv.lib.gact_quantize(xs[i].data_ptr(), nv.DTYPE_CODE[dt], n, bits, rep, mode, None, 1, pk.data_ptr(),
+                                     mn.data_ptr(), sc.data_ptr(), sp)
+                b.record(stream)
+                flush.zero_()
+                c0 = torch.cuda.Event(enable_timing=True); c0.record(stream)
+                nv.lib.gact_dequantize(pk.data_ptr(), mn.data_ptr(), sc.data_ptr(), nv.DTYPE_CODE[dt], n, bits,
+                                       out_big[(dt, n)].data_ptr(), sp)
+                c.record(stream)
+                torch.cuda.synchronize()
+                tq.append(a.elapsed_time(b)); td.append(c0.elapsed_time(c))
+            tq.sort(); td.sort()
+            table[name] = {"quantize_GBps": round(by / tq[3] / 1e6, 1), "dequantize_GBps": round(by / td[3] / 1e6, 1),
+                           "quantize_us": round(tq[3] * 1e3, 1), "dequantize_us": round(td[3] * 1e3, 1)}
+            print(f"[bench] {name:22s} quantize {tq[3]*1e3:8.1f} us {by/tq[3]/1e6:7.0f} GB/s | dequantize {td[3]*1e3:8.1f} us "
+                  f"{by/td[3]/1e6:7.0f} GB/s", file=sys.stderr)
+        del flush
+
+    # ---- end-to-end arm: pinned host -> op_quantize -> op_dequantize -> host ---------------------------------
+    # (the big tensors only share two host buffers; every step copies each case's input in and its result out)
+    e2e_spec = list(range(len(spec)))
+    host_in, host_out = {}, {}
+    for i in e2e_spec:
+        name, dt, n, bits = spec[i]
+        key = (dt, n, name.startswith("relu"))
+        if key not in host_in:
+            host_in[key] = xs[i].cpu().pin_memory()
+            host_out[key] = torch.empty(n, dtype=dt).pin_memory()
+    h2d = sum(spec[i][2] * 2 for i in e2e_spec)
+    d2h = h2d
+
+    def e2e_step(step):
+        saved = []
+        for i in e2e_spec:
+            name, dt, n, bits = spec[i]
+            key = (dt, n, name.startswith("relu"))
+            x = host_in[key].to(dev, non_blocking=True)
+            saved.append((op_quantize(x, bits, i + step), x.shape, key))
+            del x
+        for q, shape, key in reversed(saved):
+            y = op_dequantize(q, shape)
+            host_out[key].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    gact.config.rng_mode = args.rng
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    for w in range(min(args.warmup, 2)):
+        e2e_step(w)
+    barrier()
+    t0 = time.perf_counter()
+    for k in range(e2e_steps):
+        e2e_step(100 + k)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    # ---- reduce over ranks: max time, sum of bytes -----------------------------------------------------------
+    times = torch.tensor([total_ms, q_ms, d_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    total_ms, q_ms, d_ms, e2e_ms = times.tolist()
+    step_bytes = spec_bytes(spec)
+    value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
+    e2e_value = world * step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        peaks = {}
+        pk_path = ROOT / "MEASURED_PEAKS.json"
+        if pk_path.exists():
+            peaks = json.loads(pk_path.read_text())
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+        q_gbps = (step_bytes / 2) * args.steps / (q_ms * 1e-3) / 1e9
+        d_gbps = (step_bytes / 2) * args.steps / (d_ms * 1e-3) / 1e9
+        n_launch = len(spec)
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16/bf16 in, u8 codes", "data": "synthetic",
+            "config": {"workload": "kernel sweep: relu 128x64x112x112 fp16+bf16 x bits{1,2,4,8} + 50 mixed fp16 tensors 2^20..2^26 x bits{2,4,8}",
+                       "group_size": GROUP, "rng": args.rng, "l2": "inputs larger than L2; all quantizes of a step run before its dequantizes",
+                       "bytes_per_step_per_gpu": step_bytes},
+            "pct_of_8TBps": round(100 * value / world / 8000.0, 1),
+            "roofline": {"kernel": "quantize_kernel (all %d launches of a step)" % n_launch, "bound": "hbm",
+                         "achieved": round(q_gbps, 1), "peak": peak, "unit": "GB/s", "frac": round(q_gbps / peak, 3),
+                         "traffic": None, "peak_source": peak_src,
+                         "dequantize": {"achieved": round(d_gbps, 1), "frac": round(d_gbps / peak, 3)}},
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "api": "gact.ops.op_quantize/op_dequantize from pinned host buffers"},
+            "gpu_launches": 2 * n_launch * args.steps,
+            "clocks": clocks,
+            "kernels": table,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(spec, sample_elems=1 << 22, reps=1)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------------------------
+def cpu_sample(spec, sample_elems):
+    """Bounded sample of the workload for the CPU runs: the first `sample_elems` elements of the eight big cases
+    and of the first eight mixed tensors (same dtypes, widths and distributions)."""
+    g = torch.Generator().manual_seed(99)
+    base = torch.randn(sample_elems, generator=g)
+    cases = []
+    for name, dt, n, bits in spec[:16]:
+        m = min(n, sample_elems)
+        x = base[:m].clamp_min(0) if name.startswith("relu") else base[:m]
+        cases.append((name, x.to(dt).contiguous(), bits))
+    return cases
+
+
+def cpu_pass(cases, seed):
+    import oracle
+    by = 0
+    t0 = time.perf_counter()
+    for name, x, bits in cases:
+        pk, mn, sc = oracle.quantize(x, bits, seed)
+        oracle.dequantize(pk, mn, sc, x.numel(), bits)
+        by += 2 * alg_bytes(x.numel(), bits, 2, 4 if x.dtype == torch.bfloat16 else 2)
+    return by, time.perf_counter() - t0
+
+
+def cpu_baseline(spec, sample_elems, reps):
+    import oracle
+    cases = cpu_sample(spec, sample_elems)
+    cpu_pass(cases[:2], 0)
+    by, dt = 0, 0.0
+    for r in range(reps):
+        b, t = cpu_pass(cases, r)
+        by += b; dt += t
+    return {"value": round(by / dt / 1e9, 3), "unit": "GB/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"first {sample_elems} elements of the 8 big cases and of 8 mixed tensors, quantize+dequantize, "
+                      f"CPU restatement of the reference kernels (oracle/gact_oracle.c, OpenMP), {reps} pass(es), {dt:.1f} s"}
+
+
+def run_reference(args):
+    """The reference has no CPU implementation of this path (every entry point demands CUDA tensors), so its
+    arm is the CPU restatement of its kernels (the oracle), on all host threads, over a bounded sample."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    import oracle
+    spec = workload_spec()
+    sample = 1 << 22
+    cases = cpu_sample(spec, sample)
+    for w in range(args.warmup):
+        cpu_pass(cases[:4], w)
+    by, dt = 0, 0.0
+    for k in range(args.steps):
+        b, t = cpu_pass(cases, k)
+        by += b; dt += t
+    v = round(by / dt / 1e9, 3)
+    base = {"value": v, "unit": "GB/s", "cores": oracle.threads(), "kind": "port",
+            "sample": f"per step: first {sample} elements of the 8 big cases and of 8 mixed tensors, quantize+dequantize"}
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16/bf16 in, u8 codes", "data": "synthetic",
+            "config": {"workload": "kernel sweep (bounded sample on host cores)", "group_size": GROUP, "rng": "curand"},
+            "cpu_baseline": base,
+            "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rng", default="curand", choices=["curand", "fast", "rtn"])
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-table", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU baseline")
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

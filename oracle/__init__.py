@@ -27,11 +27,16 @@ _lib = None
 
 
 def build(force: bool = False) -> Path:
-    """Compile the C restatement with gcc (a second or two)."""
+    """Compile the C restatement with gcc (a second or two).  OpenMP is used when the compiler has it (it only
+    spreads independent groups over the host cores); otherwise the oracle runs on one thread."""
     if force or not _LIB.exists() or _LIB.stat().st_mtime < _SRC.stat().st_mtime:
-        cc = os.environ.get("CC", "gcc")
-        subprocess.check_call([cc, "-O2", "-fPIC", "-std=c11", "-ffp-contract=off", "-fno-fast-math",
-                               "-shared", "-o", str(_LIB), str(_SRC), "-lm"])
+        base = ["-O2", "-fPIC", "-std=c11", "-ffp-contract=off", "-fno-fast-math", "-shared", "-o", str(_LIB), str(_SRC), "-lm"]
+        compilers = [c for c in (os.environ.get("CC"), "/usr/bin/gcc", "gcc") if c]
+        for extra in (["-fopenmp"], []):
+            for cc in compilers:
+                if subprocess.run([cc] + extra + base, capture_output=True).returncode == 0:
+                    return _LIB
+        raise RuntimeError("could not compile oracle/gact_oracle.c with any of %s" % compilers)
     return _LIB
 
 
@@ -191,6 +196,15 @@ def sensitivity(d3) -> float:
     if sens != sens or sens in (float("inf"), float("-inf")) or sens > 1e10:
         return 1e10
     return sens
+
+
+def threads() -> int:
+    """Host threads the quantize / dequantize loops use (OpenMP)."""
+    return int(lib().oracle_threads())
+
+
+def set_threads(t: int) -> None:
+    lib().oracle_set_threads(int(t))
 
 
 def curand_uniform(seed: int, subsequence: int, draw: int) -> float:

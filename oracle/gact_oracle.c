@@ -20,7 +20,9 @@
  * unmodified; quantize / dequantize / mask against the reference's CUDA kernels built unmodified and
  * run on a GPU (see tests/).
  *
- * Build:  gcc -O2 -fPIC -shared -ffp-contract=off -o libgact_oracle.so gact_oracle.c -lm
+ * Build:  gcc -O2 -fPIC -shared -fopenmp -ffp-contract=off -o libgact_oracle.so gact_oracle.c -lm
+ *         (OpenMP only spreads independent groups / row-blocks over the host cores; OMP_NUM_THREADS=1
+ *         gives the scalar run.)
  *         (-ffp-contract=off matters: every rounding below is spelled out.)
  */
 #include <math.h>
@@ -246,8 +248,9 @@ int oracle_quantize(const void *x, int dtype, int64_t n, int bits, uint64_t seed
     const int64_t R = (G + wpt - 1) / wpt;
     float *mn = (float *)malloc(sizeof(float) * (size_t)(G ? G : 1));
     float *sc = (float *)malloc(sizeof(float) * (size_t)(G ? G : 1));
-    float v[GROUP];
+#pragma omp parallel for schedule(static)
     for (int64_t g = 0; g < G; g++) {
+        float v[GROUP];
         float lo, hi;
         fetch_group(x, dtype, n, g, v);
         group_minmax(v, dtype, &lo, &hi);
@@ -256,6 +259,7 @@ int oracle_quantize(const void *x, int dtype, int64_t n, int bits, uint64_t seed
         store_elem(qmin, dtype, g, mn[g]);
         store_elem(qscale, scale_dtype(dtype), g, sc[g]);
     }
+#pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < R; r++) {
         for (int d = 0; d < GROUP; d++) {
             const int64_t gid = r * GROUP + d;                 /* = the packed byte index = Philox subsequence */
@@ -306,6 +310,7 @@ int oracle_dequantize(const uint8_t *packed, const void *qmin, const void *qscal
     if (dtype < 0 || dtype > 2) return 2;
     const int wpt = 8 / bits;
     const int mask = (1 << bits) - 1;
+#pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; i++) {
         const int64_t g = i / GROUP;
         const int d = (int)(i % GROUP);
@@ -466,3 +471,12 @@ static float fast_noise(uint64_t seed, int64_t elem) {
     return ((float)h + 0.5f) * 1.52587890625e-05f;
 }
 float oracle_fast_noise(uint64_t seed, int64_t elem) { return fast_noise(seed, elem); }
+
+#ifdef _OPENMP
+#include <omp.h>
+int oracle_threads(void) { return omp_get_max_threads(); }
+void oracle_set_threads(int t) { omp_set_num_threads(t); }
+#else
+int oracle_threads(void) { return 1; }
+void oracle_set_threads(int t) { (void)t; }
+#endif
