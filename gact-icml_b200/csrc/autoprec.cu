@@ -1,5 +1,7 @@
 // Device side of the auto-precision controller: squared distances between gradient vectors, the
 // sensitivity clamp, and the greedy bit allocation.
+#include <mutex>
+
 #include "gact_common.cuh"
 
 namespace gact {
@@ -194,6 +196,42 @@ __global__ void __launch_bounds__(kPThreads) calc_precision_kernel(int32_t* __re
     if (tid == 0 && status != nullptr) *status = st;
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// gact_sq_diffs3_noalloc: the same reduction for callers that cannot allocate device memory.
+//
+// Who that is: code running inside a region where the CUDA allocator must not be touched (a framework's
+// allocator-free section, a real-time loop that forbids cudaMalloc because it synchronises the device), or a
+// host language binding that has no device allocator at hand and only holds the pointers it was given.  The
+// scratch that gact_sq_diffs3 takes from its caller lives here in a fixed array inside the library image: the
+// block partials plus a table for up to GACT_NOALLOC_MAX_SEGMENTS gradient segments.  Every GPU that loads the
+// library carries these ~62 KB until the process exits.
+//
+// In host code the array's name is only a handle for the runtime, not a device address, so the address the
+// kernels get is looked up with cudaGetSymbolAddress once per device (with that device current) and cached.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kNoAllocPartialBytes = ((kSBlocks * 3 * (int)sizeof(double) + 255) / 256) * 256;
+constexpr int kNoAllocTableBytes = GACT_NOALLOC_MAX_SEGMENTS * 8;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartialBytes + 3 * kNoAllocTableBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_noalloc_addr[kMaxDevices];          // device address of g_noalloc_scratch, per device ordinal
+static std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device; looked up on the first call per device.
+static int noalloc_scratch_address(unsigned char** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return GACT_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return GACT_ERR_LAUNCH;
+        g_noalloc_addr[dev] = p;
+    }
+    *out = (unsigned char*)g_noalloc_addr[dev];
+    return GACT_OK;
+}
+
 }  // namespace gact
 
 using namespace gact;
@@ -214,6 +252,39 @@ extern "C" int gact_sq_diffs3(const float* g0, const float* g1, const float* g2,
     else
         sq_diffs3_partial_seg_kernel<<<kSBlocks, kSThreads, 0, s>>>(g0, g1, P, seg_ptr, seg_off, seg_len, nseg, (double*)scratch);
     sq_diffs3_final_kernel<<<1, kSThreads, 0, s>>>((const double*)scratch, kSBlocks, out3);
+    return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+}
+
+extern "C" int gact_sq_diffs3_noalloc(const float* g0, const float* g1, const float* g2, int64_t P,
+                                      const float* const* seg_ptr_host, const int64_t* seg_off_host,
+                                      const int64_t* seg_len_host, int nseg, double* out3, void* stream) {
+    if (P < 0 || nseg < 0) return GACT_ERR_SIZE;
+    if (nseg > GACT_NOALLOC_MAX_SEGMENTS) return GACT_ERR_NOALLOC_LIMIT;
+    if (!g0 || !g1 || !out3) return GACT_ERR_NULL;
+    if (nseg == 0 && !g2) return GACT_ERR_NULL;
+    if (nseg > 0 && (!seg_ptr_host || !seg_off_host || !seg_len_host)) return GACT_ERR_NULL;
+    if ((uintptr_t)out3 & 7) return GACT_ERR_ALIGN;
+    unsigned char* base = nullptr;
+    const int rc = noalloc_scratch_address(&base);
+    if (rc != GACT_OK) return rc;
+    double* partials = (double*)base;               // fully rewritten by stage 1 before stage 2 reads it
+    cudaStream_t s = (cudaStream_t)stream;
+    if (nseg == 0) {
+        sq_diffs3_partial_kernel<<<kSBlocks, kSThreads, 0, s>>>(g0, g1, g2, P, partials);
+    } else {
+        unsigned char* t_ptr = base + kNoAllocPartialBytes;
+        unsigned char* t_off = t_ptr + kNoAllocTableBytes;
+        unsigned char* t_len = t_off + kNoAllocTableBytes;
+        const size_t bytes = (size_t)nseg * 8;
+        // stream-ordered copies of the caller's host tables into the library's own table
+        if (cudaMemcpyAsync(t_ptr, seg_ptr_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+            cudaMemcpyAsync(t_off, seg_off_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+            cudaMemcpyAsync(t_len, seg_len_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+            return GACT_ERR_LAUNCH;
+        sq_diffs3_partial_seg_kernel<<<kSBlocks, kSThreads, 0, s>>>(g0, g1, P, (const float* const*)t_ptr, (const int64_t*)t_off,
+                                                                   (const int64_t*)t_len, nseg, partials);
+    }
+    sq_diffs3_final_kernel<<<1, kSThreads, 0, s>>>(partials, kSBlocks, out3);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }
 
@@ -253,6 +324,7 @@ extern "C" const char* gact_error_string(int status) {
     case GACT_ERR_MODE: return "unknown rng mode, or the noise array is missing";
     case GACT_ERR_LAUNCH: return "the CUDA runtime refused the launch";
     case GACT_ERR_BUDGET: return "bit budget cannot be met";
+    case GACT_ERR_NOALLOC_LIMIT: return "more gradient segments than the allocation-free entry point holds (GACT_NOALLOC_MAX_SEGMENTS)";
     default: return "unknown status";
     }
 }

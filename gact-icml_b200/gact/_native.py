@@ -39,6 +39,7 @@ _SIGNATURES = {
     "gact_mask_unpack": ([_vp, _i64, _vp, _vp], _i),
     "gact_sq_diffs3_scratch_bytes": ([], _i64),
     "gact_sq_diffs3": ([_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _vp, _vp], _i),
+    "gact_sq_diffs3_noalloc": ([_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _vp], _i),
     "gact_sensitivity": ([_vp, _d, _vp, _i, _vp], _i),
     "gact_calc_precision": ([_vp, _vp, _vp, _i, _d, _vp, _vp], _i),
 }
@@ -58,7 +59,7 @@ def check(status: int, what: str) -> None:
     if status == 0:
         return
     msg = f"{what}: {lib.gact_error_string(status).decode()} (status {status})"
-    if status in (1, 2, 5, 6):
+    if status in (1, 2, 5, 6, 9):
         raise ValueError(msg)
     raise GactError(msg)
 

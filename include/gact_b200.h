@@ -5,8 +5,8 @@
  * (0 = GACT_OK, see gact_error_string) and never throws.  The caller owns every buffer.  Kernels are
  * enqueued on the stream passed in (a cudaStream_t, 0 = the legacy default stream) of the CURRENT device;
  * nothing synchronises with the host and nothing is allocated unless a comment says otherwise.
- * The library keeps no mutable global state, so calls may come from any thread (PyTorch runs the
- * backward-side calls on its autograd worker threads).
+ * The library keeps no mutable global state (the one exception is documented at gact_sq_diffs3_noalloc), so
+ * calls may come from any thread (PyTorch runs the backward-side calls on its autograd worker threads).
  *
  * Each declaration names the interface of the reference implementation (paths inside the GACT
  * repository) that it replaces.
@@ -48,7 +48,8 @@ enum {
     GACT_ERR_SIZE = 5,       /* negative or unsupported size */
     GACT_ERR_MODE = 6,       /* unknown rng mode / missing noise array */
     GACT_ERR_LAUNCH = 7,     /* the CUDA runtime refused the launch (cudaGetLastError) */
-    GACT_ERR_BUDGET = 8      /* greedy allocation: budget cannot be met even at 1 bit everywhere */
+    GACT_ERR_BUDGET = 8,     /* greedy allocation: budget cannot be met even at 1 bit everywhere */
+    GACT_ERR_NOALLOC_LIMIT = 9 /* gact_sq_diffs3_noalloc: more segments than GACT_NOALLOC_MAX_SEGMENTS */
 };
 
 int gact_version(void);
@@ -125,6 +126,34 @@ int64_t gact_sq_diffs3_scratch_bytes(void);
 int gact_sq_diffs3(const float* g0, const float* g1, const float* g2, int64_t P,
                    const float* const* seg_ptr, const int64_t* seg_off, const int64_t* seg_len, int nseg,
                    void* scratch, double* out3, void* stream);
+
+/*
+ * gact_sq_diffs3 for callers that cannot allocate device memory.  (No counterpart in the reference, which
+ * concatenates the gradients and lets PyTorch allocate every temporary.)
+ *
+ * Some callers only hold the pointers they were handed: code inside a section where the device allocator
+ * must stay untouched (cudaMalloc synchronises the whole device, which a latency-bound loop cannot afford), or
+ * a binding from a host language that has no device allocator to ask.  For them the scratch of
+ * gact_sq_diffs3 - the block partials and the segment table - sits in a fixed array inside the library image,
+ * about 62 KB that every GPU using the library holds until the process exits.  This entry point calls no
+ * cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Differences from gact_sq_diffs3: no `scratch` argument; the three segment tables are HOST arrays
+ * (seg_ptr_host[k] is still a device pointer), copied by the call itself, in stream order, into the library's
+ * table, so they may be reused as soon as the call returns.  Limit: nseg <= GACT_NOALLOC_MAX_SEGMENTS, else
+ * GACT_ERR_NOALLOC_LIMIT and nothing is launched; P is not limited.  nseg = 0 selects the contiguous g2.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current) and caches it; make that first call outside of any stream capture.  All calls on a device share the
+ * one array, which simply keeps what the last call left in it; nothing in it has to start at zero, because
+ * every call rewrites the partials and the table entries it reads before reading them.  For the same reason
+ * two calls that overlap on the GPU (different streams, or different threads on different streams) race on it:
+ * issue them on one stream, or order them with events.
+ */
+#define GACT_NOALLOC_MAX_SEGMENTS 2048
+int gact_sq_diffs3_noalloc(const float* g0, const float* g1, const float* g2, int64_t P,
+                           const float* const* seg_ptr_host, const int64_t* seg_off_host,
+                           const int64_t* seg_len_host, int nseg, double* out3, void* stream);
 
 /*
  * Sensitivities from the distances, on the device, for L tensors at once: with (d01, d02, d12) =
