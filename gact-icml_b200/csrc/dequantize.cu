@@ -1,13 +1,24 @@
 // Unpack + dequantize: out = T(T(code) / scale) + min, written for the first n elements only.
 //
-// A warp owns U row-blocks of the packed layout.  Each lane reads its 8 packed bytes per row-block with
-// one 8-byte (16-bit outputs) or two 4-byte (fp32) loads, and for each of the wpt groups of the row-block
-// writes 8 output values with one or two 16-byte streaming stores.
+// A warp owns a tile of GPW = max(4, wpt) groups = U row-blocks of the packed layout.  Each lane reads its 8
+// packed bytes per row-block with one 8-byte load - all loads of the
+// tile first - and writes 8 output values per group with one streaming store (16 bytes, or 32 bytes for fp32).
+//
+// No per-element division.  The quotient code/scale is formed from one reciprocal per group:
+//   fp16:  round_h(fl32(code * fl32(1/scale))) equals round_h(fl32(code / scale)) for every half-precision
+//          scale and every code 0..255 (checked exhaustively, 65 536 x 256 cases, by the CPU test-suite);
+//   fp32 / bf16 (fp32 scale):  q0 = code*r, e = fma(-q0, scale, code), q = fma(e, r, q0) with r = fl32(1/scale)
+//          is the correctly rounded quotient for all 2^23 significands of scale and codes 1..255 (checked
+//          exhaustively for one binade, sampled over the others); scales outside 2^-60..2^60, zero, infinite,
+//          negative or NaN take the IEEE division instead (a warp-uniform branch).
+// Codes become floats without a conversion instruction: a byte permute drops the code into the low mantissa
+// bits of 2^23, and the 2^23 is folded into the following multiply-add.
 #include "gact_common.cuh"
 
 namespace gact {
 
 constexpr int kDThreads = 256;
+constexpr float kTwo23 = 8388608.0f;
 
 struct DequantArgs {
     const uint8_t* packed;
@@ -15,33 +26,22 @@ struct DequantArgs {
     const void* qscale;
     int64_t n, G, R;
     void* out;
+    int aligned32;
 };
 
+// 2^23 + (byte `idx` of w) as a float bit pattern: bytes {w[idx], 0x00, 0x00, 0x4B}
+__device__ __forceinline__ float byte_as_magic(uint32_t w, int idx) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u + (uint32_t)idx));
+}
+
 template <int DT>
-__device__ __forceinline__ void store_group8(void* out, int64_t n, int64_t g, int lane, const float (&o)[8]) {
+__device__ __forceinline__ void store_group8_slow(void* out, int64_t n, int64_t g, int lane, const float (&o)[8]) {
     using E = Elem<DT>;
     using T = typename E::T;
-    const int64_t base = g * kGroup;
-    if (base + kGroup <= n) {
-        if (DT == GACT_F32) {
-            float* p = (float*)out + base + lane * 4;
-            st_stream_u4(p, make_uint4(__float_as_uint(o[0]), __float_as_uint(o[1]), __float_as_uint(o[2]), __float_as_uint(o[3])));
-            st_stream_u4(p + 128, make_uint4(__float_as_uint(o[4]), __float_as_uint(o[5]), __float_as_uint(o[6]), __float_as_uint(o[7])));
-        } else {
-            uint32_t w[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const T a = E::from_float(o[2 * i]), b = E::from_float(o[2 * i + 1]);
-                w[i] = (uint32_t)(*(const uint16_t*)&a) | ((uint32_t)(*(const uint16_t*)&b) << 16);
-            }
-            st_stream_u4((uint16_t*)out + base + lane * 8, make_uint4(w[0], w[1], w[2], w[3]));
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const int64_t i = base + elem_pos<DT>(lane, j);
-            if (i < n) ((T*)out)[i] = E::from_float(o[j]);
-        }
+    for (int j = 0; j < 8; j++) {
+        const int64_t i = g * kGroup + elem_pos<DT>(lane, j);
+        if (i < n) ((T*)out)[i] = E::from_float(o[j]);
     }
 }
 
@@ -50,49 +50,118 @@ __global__ void __launch_bounds__(kDThreads) dequantize_kernel(const DequantArgs
     using E = Elem<DT>;
     using T = typename E::T;
     constexpr int WPT = 8 / BITS;
-    constexpr uint32_t MASK = (1u << BITS) - 1u;
+    constexpr int U = (WPT >= 4) ? 1 : 4 / WPT;
+    constexpr int GPW = WPT * U;
+    constexpr uint32_t MASK4 = ((1u << BITS) - 1u) * 0x01010101u;
     const int lane = threadIdx.x & 31;
     const int64_t nwarps = (int64_t)gridDim.x * (kDThreads / 32);
+    const int64_t tiles = (a.R + U - 1) / U;
 
-    for (int64_t r = (int64_t)blockIdx.x * (kDThreads / 32) + (threadIdx.x >> 5); r < a.R; r += nwarps) {
-        const uint8_t* row = a.packed + r * kGroup;
-        uint32_t lo, hi;
-        if (DT == GACT_F32) {
-            lo = ld_stream_u1(row + lane * 4);
-            hi = ld_stream_u1(row + 128 + lane * 4);
-        } else {
-            const uint2 p = ld_stream_u2(row + lane * 8);
-            lo = p.x; hi = p.y;
-        }
-        // one (scale, min) pair per group of the row-block: lane i fetches group i's, then broadcast
-        float my_s = 0.0f, my_m = 0.0f;
-        const int64_t gl = r * WPT + lane;
-        if (lane < WPT && gl < a.G) {
-            my_s = load_scale<DT>(a.qscale, gl);
-            my_m = E::to_float(((const T*)a.qmin)[gl]);
-        }
+    for (int64_t tile = (int64_t)blockIdx.x * (kDThreads / 32) + (threadIdx.x >> 5); tile < tiles; tile += nwarps) {
+        const int64_t g0 = tile * GPW;
+        uint32_t lo[U], hi[U];
 #pragma unroll
-        for (int ni = 0; ni < WPT; ni++) {
-            const int64_t g = r * WPT + ni;
-            if (g >= a.G) break;
-            const float s = __shfl_sync(kFull, my_s, ni), m = __shfl_sync(kFull, my_m, ni);
-            float o[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const uint32_t word = (j < 4) ? lo : hi;
-                const uint32_t code = (word >> ((j & 3) * 8 + ni * BITS)) & MASK;
-                const float c = (float)code;                           // exact in every T (<= 255)
-                o[j] = (DT != GACT_F16) ? __fadd_rn(__fdiv_rn(c, s), m)
-                                        : __fadd_rn(E::round(__fdiv_rn(c, s)), m);   // final rounding on store
+        for (int u = 0; u < U; u++) {
+            const int64_t r = tile * U + u;
+            lo[u] = hi[u] = 0;
+            if (r < a.R) {
+                const uint2 p = ld_stream_u2(a.packed + r * kGroup + lane * 8);
+                lo[u] = p.x; hi[u] = p.y;
             }
-            store_group8<DT>(a.out, a.n, g, lane, o);
+        }
+        // lane k < GPW fetches scale and min of group g0+k and forms the reciprocal once
+        float my_s = 1.0f, my_m = 0.0f;
+        if (lane < GPW && g0 + lane < a.G) {
+            my_s = load_scale<DT>(a.qscale, g0 + lane);
+            my_m = E::to_float(((const T*)a.qmin)[g0 + lane]);
+        }
+        const float my_r = __fdiv_rn(1.0f, my_s);
+
+#pragma unroll
+        for (int k = 0; k < GPW; k++) {
+            const int64_t g = g0 + k;
+            if (g >= a.G) break;
+            const int u = k / WPT, ni = k % WPT;
+            const float s = __shfl_sync(kFull, my_s, k), m = __shfl_sync(kFull, my_m, k), r = __shfl_sync(kFull, my_r, k);
+            // this group's codes as bytes: (w >> ni*BITS) & mask, four elements per word
+            const uint32_t c_lo = (BITS == 8) ? lo[u] : ((lo[u] >> (ni * BITS)) & MASK4);
+            const uint32_t c_hi = (BITS == 8) ? hi[u] : ((hi[u] >> (ni * BITS)) & MASK4);
+            const bool full = (g + 1) * kGroup <= a.n;
+
+            if (DT == GACT_F16) {
+                // q = round_h(code * r), out = round_h(q + m): two elements per instruction after the multiply
+                const float bias = -kTwo23 * r;                       // exact (power-of-two scaling); may be -inf/NaN with r
+                const __half2 m2 = __float2half2_rn(m);
+                uint32_t w[4];
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const uint32_t word = (j < 4) ? c_lo : c_hi;
+                    float q0, q1;
+                    if (isfinite(bias)) {
+                        q0 = __fmaf_rn(byte_as_magic(word, j & 3), r, bias);          // = fl32(code * r)
+                        q1 = __fmaf_rn(byte_as_magic(word, (j + 1) & 3), r, bias);
+                    } else {                                                          // r is inf or NaN (scale 0 / NaN)
+                        q0 = __fmul_rn(byte_as_magic(word, j & 3) - kTwo23, r);
+                        q1 = __fmul_rn(byte_as_magic(word, (j + 1) & 3) - kTwo23, r);
+                    }
+                    const __half2 h = __hadd2(__floats2half2_rn(q0, q1), m2);
+                    w[j >> 1] = *(const uint32_t*)&h;
+                    if (!full) { const float2 f = __half22float2(h); o[j] = f.x; o[j + 1] = f.y; }
+                }
+                if (full) st_stream_u4((uint16_t*)a.out + g * kGroup + lane * 8, make_uint4(w[0], w[1], w[2], w[3]));
+                else store_group8_slow<DT>(a.out, a.n, g, lane, o);
+            } else {
+                // correctly rounded fp32 quotient from the reciprocal (Markstein); IEEE division for unusual scales
+                const uint32_t sb = __float_as_uint(s);
+                const bool fast = (sb - 0x21800000u) < (0x5D800000u - 0x21800000u);   // 2^-60 <= s < 2^60, s > 0
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const uint32_t word = (j < 4) ? c_lo : c_hi;
+                    const float c = byte_as_magic(word, j & 3) - kTwo23;              // exact
+                    float q;
+                    if (fast) {
+                        const float q0 = __fmul_rn(c, r);
+                        const float e = __fmaf_rn(-q0, s, c);
+                        q = __fmaf_rn(e, r, q0);
+                    } else {
+                        q = __fdiv_rn(c, s);
+                    }
+                    o[j] = __fadd_rn(q, m);
+                }
+                if (!full) {
+                    store_group8_slow<DT>(a.out, a.n, g, lane, o);
+                } else if (DT == GACT_F32) {
+                    float* p = (float*)a.out + g * kGroup + lane * 8;
+                    if (a.aligned32) {
+                        const uint32_t w[8] = {__float_as_uint(o[0]), __float_as_uint(o[1]), __float_as_uint(o[2]), __float_as_uint(o[3]),
+                                               __float_as_uint(o[4]), __float_as_uint(o[5]), __float_as_uint(o[6]), __float_as_uint(o[7])};
+                        st_stream_u8(p, w);
+                    } else {
+                        st_stream_u4(p, make_uint4(__float_as_uint(o[0]), __float_as_uint(o[1]), __float_as_uint(o[2]), __float_as_uint(o[3])));
+                        st_stream_u4(p + 4, make_uint4(__float_as_uint(o[4]), __float_as_uint(o[5]), __float_as_uint(o[6]), __float_as_uint(o[7])));
+                    }
+                } else {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const __nv_bfloat162 b = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+                        w[i] = *(const uint32_t*)&b;
+                    }
+                    st_stream_u4((uint16_t*)a.out + g * kGroup + lane * 8, make_uint4(w[0], w[1], w[2], w[3]));
+                }
+            }
         }
     }
 }
 
 template <int DT, int BITS> static int launch_dequantize(const DequantArgs& a, cudaStream_t s) {
-    const int64_t want = (a.R + kDThreads / 32 - 1) / (kDThreads / 32);
-    const int64_t cap = (int64_t)kSMs * 8;
+    constexpr int WPT = 8 / BITS;
+    constexpr int U = (WPT >= 4) ? 1 : 4 / WPT;
+    const int64_t tiles = (a.R + U - 1) / U;
+    const int64_t want = (tiles + kDThreads / 32 - 1) / (kDThreads / 32);
+    const int64_t cap = (int64_t)kSMs * 16;
     const int blocks = (int)(want < cap ? want : cap);
     dequantize_kernel<DT, BITS><<<blocks, kDThreads, 0, s>>>(a);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
@@ -125,6 +194,7 @@ extern "C" int gact_dequantize(const void* packed, const void* qmin, const void*
     a.G = (n + kGroup - 1) / kGroup;
     a.R = (a.G + 8 / bits - 1) / (8 / bits);
     a.out = out;
+    a.aligned32 = ((uintptr_t)out & 31) ? 0 : 1;
     cudaStream_t s = (cudaStream_t)stream;
     switch (dtype) {
     case GACT_F32: return dispatch_dq<GACT_F32>(a, bits, s);

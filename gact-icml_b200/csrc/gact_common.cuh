@@ -75,21 +75,22 @@ template <> struct Elem<GACT_BF16> {
     static __device__ __forceinline__ float init_hi() { return __bfloat162float(__float2bfloat16_rn(1e30f)); }
 };
 
-// Position inside a 256-element group of the j-th (0..7) value a lane holds.
-//   16-bit types: one 16-byte load per lane, d = lane*8 + j.
-//   fp32: two 16-byte loads per lane, each fully coalesced across the warp:
-//         d = lane*4 + j (j < 4) and 128 + lane*4 + (j-4).
-template <int DT> __device__ __forceinline__ int elem_pos(int lane, int j) {
-    if (DT == GACT_F32) return (j < 4) ? lane * 4 + j : 128 + lane * 4 + (j - 4);
-    return lane * 8 + j;
-}
+// Every lane of a warp holds 8 consecutive values of a 256-element group: position d = lane*8 + j.
+// That is one 16-byte access per lane for the 16-bit types and one 32-byte (256-bit) access for fp32, both
+// fully coalesced, and it makes a lane's 8 packed bytes of a row-block contiguous as well.
+template <int DT> __device__ __forceinline__ int elem_pos(int lane, int j) { return lane * 8 + j; }
 
-// Streaming 128-bit accesses: the data is touched once, keep it out of L1.
+// Streaming accesses: the data is touched once, keep it out of L1.
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
+}
+// 256-bit load (sm_100): 8 consecutive 32-bit words, 32-byte aligned
+__device__ __forceinline__ void ld_stream_u8(const void* p, uint32_t (&v)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "l"(p));
 }
 __device__ __forceinline__ uint2 ld_stream_u2(const void* p) {
     uint2 v;
@@ -104,6 +105,10 @@ __device__ __forceinline__ uint32_t ld_stream_u1(const void* p) {
 __device__ __forceinline__ void st_stream_u4(void* p, uint4 v) {
     asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+__device__ __forceinline__ void st_stream_u8(void* p, const uint32_t (&v)[8]) {
+    asm volatile("st.global.cs.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+                 "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
 __device__ __forceinline__ void st_stream_u2(void* p, uint2 v) {
     asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
@@ -111,49 +116,85 @@ __device__ __forceinline__ void st_stream_u1(void* p, uint32_t v) {
     asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Load the 8 values of group `g` that belong to `lane`, as floats (exact widening for 16-bit types).
+// Number of 32-bit registers holding a lane's 8 values in storage format.
+template <int DT> struct RawRegs { static constexpr int N = (DT == GACT_F32) ? 8 : 4; };
+
+// The 8 values of group `g` that belong to `lane`, in storage format (fp32: 8 words; 16-bit: 4 packed pairs).
 // Elements at or past n read as +0 (the reference pads with real zeros, gact/gact/ops.py:12-19).
+// `aligned32`: the base pointer is 32-byte aligned (needed by the 256-bit fp32 load).
 template <int DT>
-__device__ __forceinline__ void load_group8(const void* x, int64_t n, int64_t g, int lane, float (&v)[8]) {
-    using E = Elem<DT>;
+__device__ __forceinline__ void load_raw(const void* x, int64_t n, int64_t g, int lane, bool aligned32,
+                                         uint32_t (&raw)[RawRegs<DT>::N]) {
     const int64_t base = g * kGroup;
     if (base + kGroup <= n) {
-        if (DT == GACT_F32) {
-            const float* p = (const float*)x + base + lane * 4;
-            const uint4 a = ld_stream_u4(p), b = ld_stream_u4(p + 128);
-            v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
-            v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+        if constexpr (DT == GACT_F32) {
+            const float* p = (const float*)x + base + lane * 8;
+            if (aligned32) {
+                ld_stream_u8(p, raw);
+            } else {
+                const uint4 a = ld_stream_u4(p), b = ld_stream_u4(p + 4);
+                raw[0] = a.x; raw[1] = a.y; raw[2] = a.z; raw[3] = a.w; raw[4] = b.x; raw[5] = b.y; raw[6] = b.z; raw[7] = b.w;
+            }
         } else {
             const uint4 a = ld_stream_u4((const uint16_t*)x + base + lane * 8);
-            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                if (DT == GACT_F16) {
-                    const float2 f = __half22float2(*(const __half2*)&w[i]);
-                    v[2 * i] = f.x; v[2 * i + 1] = f.y;
-                } else {
-                    v[2 * i] = __uint_as_float(w[i] << 16);
-                    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-                }
-            }
+            raw[0] = a.x; raw[1] = a.y; raw[2] = a.z; raw[3] = a.w;
         }
     } else {
 #pragma unroll
+        for (int i = 0; i < RawRegs<DT>::N; i++) raw[i] = 0;
+#pragma unroll
         for (int j = 0; j < 8; j++) {
-            const int64_t i = base + elem_pos<DT>(lane, j);
-            v[j] = (i < n) ? E::to_float(((const typename E::T*)x)[i]) : 0.0f;
+            const int64_t i = base + lane * 8 + j;
+            if (i < n) {
+                if constexpr (DT == GACT_F32) raw[j] = ((const uint32_t*)x)[i];
+                else raw[j >> 1] |= (uint32_t)((const uint16_t*)x)[i] << ((j & 1) * 16);
+            }
         }
     }
+}
+
+// storage format -> 8 floats (exact widening)
+template <int DT>
+__device__ __forceinline__ void raw_to_float(const uint32_t (&raw)[RawRegs<DT>::N], float (&v)[8]) {
+#pragma unroll
+    for (int i = 0; i < RawRegs<DT>::N; i++) {
+        if constexpr (DT == GACT_F32) {
+            v[i] = __uint_as_float(raw[i]);
+        } else if constexpr (DT == GACT_F16) {
+            const float2 f = __half22float2(*(const __half2*)&raw[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        } else {
+            v[2 * i] = __uint_as_float(raw[i] << 16);
+            v[2 * i + 1] = __uint_as_float(raw[i] & 0xffff0000u);
+        }
+    }
+}
+
+// Load the 8 values of group `g` that belong to `lane`, as floats.
+template <int DT>
+__device__ __forceinline__ void load_group8(const void* x, int64_t n, int64_t g, int lane, float (&v)[8]) {
+    uint32_t raw[RawRegs<DT>::N];
+    load_raw<DT>(x, n, g, lane, false, raw);
+    raw_to_float<DT>(raw, v);
+}
+
+// warp-wide float min / max in one instruction each (sm_100a); NaN inputs are ignored, -0 orders below +0
+__device__ __forceinline__ float warp_min_f32(float v) {
+    float r;
+    asm volatile("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ float warp_max_f32(float v) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
 }
 
 // Warp-wide min and max of per-lane candidates.  Hardware min/max ignore NaN operands and order
 // -0 below +0, so the result is the numeric extreme with a deterministic zero sign.
 __device__ __forceinline__ void warp_minmax(float& mn, float& mx) {
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) {
-        mn = fminf(mn, __shfl_xor_sync(kFull, mn, o));
-        mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, o));
-    }
+    mn = warp_min_f32(mn);
+    mx = warp_max_f32(mx);
 }
 
 // Which zero (+0 or -0) the reference's reduction order reports when the extreme of a group is zero.
@@ -176,6 +217,14 @@ __device__ __forceinline__ float zero_sign_like_reference(const float (&v)[8], i
     return __uint_as_float((best & 1u) << 31);
 }
 
+// A zero extreme can be +0 or -0 depending on the reference's reduction order.  The hardware reduction
+// reports -0 for the min when any -0 is present and +0 for the max when any +0 is present, so the answer is
+// only open when the min is -0, or the max is +0 while the min is not +0 (an all-(+0) group has min = max = +0).
+__device__ __forceinline__ bool zero_sign_ambiguous(float mn, float mx) {
+    const uint32_t bmn = __float_as_uint(mn), bmx = __float_as_uint(mx);
+    return bmn == 0x80000000u || (bmx == 0u && bmn != 0u);
+}
+
 // Per-group min and max exactly as the reference reports them (including the start values +-1e30 in T,
 // NaN elements ignored, and the sign of a zero extreme).
 template <int DT>
@@ -186,10 +235,39 @@ __device__ __forceinline__ void group_minmax(const float (&v)[8], int lane, floa
 #pragma unroll
     for (int j = 0; j < 8; j++) { mn = fminf(mn, v[j]); mx = fmaxf(mx, v[j]); }
     warp_minmax(mn, mx);
-    const uint32_t bmn = __float_as_uint(mn), bmx = __float_as_uint(mx);
-    // ambiguous only when a zero extreme could be either sign: a -0 is present in a group whose min is 0,
-    // or the max is 0 and the group is not all +0.
-    if (bmn == 0x80000000u || (bmx == 0u && bmn != 0u)) {
+    if (zero_sign_ambiguous(mn, mx)) {
+        const float z = zero_sign_like_reference<DT>(v, lane);
+        if (mn == 0.0f) mn = z;
+        if (mx == 0.0f) mx = z;
+    }
+}
+
+// Same, from the storage format.  16-bit types reduce their four packed pairs with two-wide min / max first.
+template <int DT>
+__device__ __forceinline__ void group_minmax_raw(const uint32_t (&raw)[RawRegs<DT>::N], int lane, float& mn, float& mx) {
+    const float hi = Elem<DT>::init_hi();
+    if constexpr (DT == GACT_F32) {
+        mn = hi; mx = -hi;
+#pragma unroll
+        for (int j = 0; j < 8; j++) { mn = fminf(mn, __uint_as_float(raw[j])); mx = fmaxf(mx, __uint_as_float(raw[j])); }
+    } else if constexpr (DT == GACT_F16) {
+        const __half2* h = (const __half2*)raw;
+        const __half2 lo = __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]));
+        const __half2 up = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+        const float2 a = __half22float2(lo), b = __half22float2(up);
+        mn = fminf(hi, fminf(a.x, a.y)); mx = fmaxf(-hi, fmaxf(b.x, b.y));
+    } else {
+        const __nv_bfloat162* h = (const __nv_bfloat162*)raw;
+        const __nv_bfloat162 lo = __hmin2(__hmin2(h[0], h[1]), __hmin2(h[2], h[3]));
+        const __nv_bfloat162 up = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+        const uint32_t l = *(const uint32_t*)&lo, u = *(const uint32_t*)&up;
+        mn = fminf(hi, fminf(__uint_as_float(l << 16), __uint_as_float(l & 0xffff0000u)));
+        mx = fmaxf(-hi, fmaxf(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u)));
+    }
+    warp_minmax(mn, mx);
+    if (zero_sign_ambiguous(mn, mx)) {
+        float v[8];
+        raw_to_float<DT>(raw, v);
         const float z = zero_sign_like_reference<DT>(v, lane);
         if (mn == 0.0f) mn = z;
         if (mx == 0.0f) mx = z;
@@ -198,9 +276,11 @@ __device__ __forceinline__ void group_minmax(const float (&v)[8], int lane, floa
 
 // scale = T( double(T(2^b - 1)) / (double(T(mx - mn)) + 2e-6) ), quantization_cuda_kernel.cu:33.
 // fp16 reaches T through float, as c10::Half only constructs from float.  bf16 inputs (which the reference
-// does not handle) run the fp32 pipeline on widened values and keep their scale in fp32.
+// does not handle) run the fp32 pipeline on widened values: scale = fl32((2^b-1) / fl32(fl32(mx-mn) + 2e-6f)),
+// kept in fp32.
 template <int DT> __device__ __forceinline__ float compute_scale(float mn, float mx, int bits) {
     const float d = __fsub_rn(mx, mn);
+    if (DT == GACT_BF16) return __fdiv_rn((float)((1 << bits) - 1), __fadd_rn(d, 2e-6f));
     const float r = (DT == GACT_F16) ? Elem<DT>::round(d) : d;
     const double q = (double)(float)((1 << bits) - 1) / ((double)r + 2e-6);
     const float s = __double2float_rn(q);

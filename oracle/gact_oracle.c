@@ -196,9 +196,14 @@ static void fetch_group(const void *x, int dtype, int64_t n, int64_t g, float v[
 /* scale = T( double(T(2^b-1)) / (double(T(mx-mn)) + 2e-6) ), quantization_cuda_kernel.cu:33.
  * fp16: the double result reaches T through float (c10::Half only constructs from float).
  * bf16 (no counterpart in the reference, which skips bf16 tensors): the whole pipeline runs in fp32 on the
- * widened values and the scale is KEPT in fp32, because a scale rounded to 8 significant bits would push
- * the largest element of a group past 2^b - 1. */
+ * widened values: scale = fl32((2^b-1) / fl32(fl32(mx-mn) + 2e-6f)), KEPT in fp32, because a scale rounded to
+ * 8 significant bits would push the largest element of a group past 2^b - 1. */
 static float compute_scale(float mn, float mx, int bits, int dtype) {
+    if (dtype == DT_BF16) {                       /* ours: fp32 throughout */
+        float d = mx - mn;
+        float den = d + 2e-6f;
+        return (float)((1 << bits) - 1) / den;
+    }
     float r = (dtype == DT_F16) ? round_T(mx - mn, dtype) : (mx - mn);
     double q = (double)(float)((1 << bits) - 1) / ((double)r + 2e-6);
     return (dtype == DT_F16) ? round_T((float)q, dtype) : (float)q;

@@ -95,6 +95,16 @@ def test_round_to_nearest_and_external_noise(dtype, bits):
     check_case(x, bits, 0, "external", noise=noise)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bits", BITS)
+def test_fast_noise_arrangement(dtype, bits):
+    """rng_mode 'fast': the same arithmetic on a different Philox arrangement (one call per 8 elements)."""
+    for n in (1, 300, 256 * 13, 256 * 64 + 5):
+        check_case(make_input("randn", n, dtype, seed=n), bits, seed=n + (7 << 33), rng_mode="fast")
+    check_case(make_input("special", 256 * 37 + 19, dtype, seed=3), bits, seed=11, rng_mode="fast")
+    check_case(make_input("relu", 256 * 5000 + 3, dtype, seed=3), bits, seed=2, rng_mode="fast")
+
+
 @pytest.mark.parametrize("bits", BITS)
 def test_fp32_unfused_multiply_add(bits):
     x = make_input("randn", 256 * 40 + 3, torch.float32, seed=8)
