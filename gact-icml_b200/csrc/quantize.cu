@@ -29,39 +29,36 @@ struct QuantArgs {
     void* qmin;
     void* qscale;
     int aligned32;
+    PhiloxKeys rk;
 };
 
+#ifndef GACT_GPW16
+#define GACT_GPW16 8
+#endif
 template <int DT, int BITS> struct Tile {
     static constexpr int WPT = 8 / BITS;
-    static constexpr int GPW = (DT == GACT_F32) ? (WPT > 4 ? WPT : 4) : 8;
+    static constexpr int GPW = (DT == GACT_F32) ? (WPT > 4 ? WPT : 4) : (WPT > GACT_GPW16 ? WPT : GACT_GPW16);
     static constexpr int U = GPW / WPT;
 };
 
-// rint(max(u - 0.5, 0)) as magic bits (code in the low bits).  `u` must not be NaN unless NANSAFE.
-template <bool NANSAFE> __device__ __forceinline__ uint32_t round_code(float u) {
-    float w = __fadd_rn(u, -0.5f);
-    if (NANSAFE) w = fmaxf(w, 0.0f);                 // NaN -> 0; negatives round to (-)0 anyway
-    return __float_as_uint(__fadd_rn(w, kMagic));
-}
-
 // noise of the FAST arrangement for the 8 elements [8*block, 8*block+8): one Philox4x32-10 call, counter
 // (block_lo, block_hi, 0, "FAST"), 16 bits per element, noise = (h + 0.5) * 2^-16
-__device__ __forceinline__ void fast_noise8(uint64_t block, uint32_t key0, uint32_t key1, float (&nz)[8]) {
-    const uint4 r = philox4x32_10((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, key0, key1);
+__device__ __forceinline__ void fast_noise8(uint64_t block, const PhiloxKeys& rk, float2 (&nz)[4]) {
+    const uint4 r = philox4x32_10((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        // 2^23 + h as a float, then (2^23 + h) * 2^-16 - (2^7 - 2^-17) = (h + 0.5) * 2^-16, exact
-        const float lo = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7410u));
-        const float hi = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7432u));
-        nz[2 * i] = __fmaf_rn(lo, 1.52587890625e-05f, -127.99999237060546875f);
-        nz[2 * i + 1] = __fmaf_rn(hi, 1.52587890625e-05f, -127.99999237060546875f);
+        // both halfwords to float on the conversion unit (no shift / mask), then (h + 0.5) * 2^-16, exact
+        float lo, hi;
+        asm("{ .reg .b16 l, h; mov.b32 {l, h}, %2; cvt.rn.f32.u16 %0, l; cvt.rn.f32.u16 %1, h; }" : "=f"(lo), "=f"(hi) : "r"(w[i]));
+        nz[i] = fma2(make_float2(lo, hi), splat2(1.52587890625e-05f), splat2(7.62939453125e-06f));
     }
 }
 
-// magic bits of the 8 codes of one group held by this lane
+// magic bits (code in the low mantissa bits of 1.5*2^23 + code) of the 8 codes of one group held by this
+// lane; nz[i] = noise of elements 2i, 2i+1
 template <int DT, int BITS, bool FMA>
-__device__ __forceinline__ void codes8(const uint32_t (&raw)[RawRegs<DT>::N], float mn, float sc, const float (&nz)[8],
+__device__ __forceinline__ void codes8(const uint32_t (&raw)[RawRegs<DT>::N], float mn, float sc, const float2 (&nz)[4],
                                        uint32_t (&cb)[8]) {
     if constexpr (DT == GACT_F16) {
         if (isinf(sc)) {
@@ -79,150 +76,186 @@ __device__ __forceinline__ void codes8(const uint32_t (&raw)[RawRegs<DT>::N], fl
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const __half2 t = __hsub2(*(const __half2*)&raw[i], mn2);
-            const __half2 p = __hmax2(__hmul2(t, sc2), zero2);                    // NaN -> 0
-            const float2 f = __half22float2(p);
-            cb[2 * i] = round_code<false>(__fadd_rn(f.x, nz[2 * i]));
-            cb[2 * i + 1] = round_code<false>(__fadd_rn(f.y, nz[2 * i + 1]));
+            const __half2 p = __hmax2(__hmul2(t, sc2), zero2);                    // NaN -> 0, as max(., 0) does
+            // u = p + noise; w = u - 0.5 (> -0.5, so no clamp needed: it rounds to 0); w + magic
+            const float2 r = add2(add2(add2(__half22float2(p), nz[i]), splat2(-0.5f)), splat2(kMagic));
+            cb[2 * i] = __float_as_uint(r.x);
+            cb[2 * i + 1] = __float_as_uint(r.y);
         }
     } else {
         float v[8];
         raw_to_float<DT>(raw, v);
+        const float2 nmn = splat2(-mn), sc2 = splat2(sc);
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const float t = __fsub_rn(v[j], mn);
-            const float u = (FMA || DT == GACT_BF16) ? __fmaf_rn(t, sc, nz[j]) : __fadd_rn(__fmul_rn(t, sc), nz[j]);
+        for (int i = 0; i < 4; i++) {
+            const float2 t = add2(make_float2(v[2 * i], v[2 * i + 1]), nmn);          // x - mn
+            const float2 u = (FMA || DT == GACT_BF16) ? fma2(t, sc2, nz[i]) : add2(mul2(t, sc2), nz[i]);
+            float2 w = add2(u, splat2(-0.5f));
+            w.x = fmaxf(w.x, 0.0f); w.y = fmaxf(w.y, 0.0f);                           // NaN -> 0
             if (DT == GACT_BF16) {
                 // ours: clamp at 2^bits - 1 (fp32 / fp16 keep the reference's missing clamp)
-                const float w = fminf(fmaxf(__fadd_rn(u, -0.5f), 0.0f), (float)((1 << BITS) - 1));
-                cb[j] = __float_as_uint(__fadd_rn(w, kMagic));
-            } else {
-                cb[j] = round_code<true>(u);
+                w.x = fminf(w.x, (float)((1 << BITS) - 1)); w.y = fminf(w.y, (float)((1 << BITS) - 1));
             }
+            const float2 r = add2(w, splat2(kMagic));
+            cb[2 * i] = __float_as_uint(r.x);
+            cb[2 * i + 1] = __float_as_uint(r.y);
         }
     }
 }
 
-template <int DT, int BITS, int RNG, bool FMA>
-__global__ void __launch_bounds__(kQThreads) quantize_kernel(const QuantArgs a) {
+// All loads of one tile (issued back to back, nothing waits on them here).  FULL: every group of the tile
+// exists and is complete, so no bounds are tested.
+template <int DT, int BITS, bool FULL>
+__device__ __forceinline__ void load_tile(const QuantArgs& a, int64_t tile, int lane,
+                                          uint32_t (&raw)[Tile<DT, BITS>::GPW][RawRegs<DT>::N]) {
+    constexpr int GPW = Tile<DT, BITS>::GPW, NR = RawRegs<DT>::N;
+    const int64_t g0 = tile * GPW;
+#pragma unroll
+    for (int k = 0; k < GPW; k++) {
+        if (FULL) {
+            load_raw<DT>(a.x, (g0 + GPW) * kGroup, g0 + k, lane, a.aligned32 != 0, raw[k]);
+        } else if (g0 + k < a.G) {
+            load_raw<DT>(a.x, a.n, g0 + k, lane, a.aligned32 != 0, raw[k]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NR; i++) raw[k][i] = 0;
+        }
+    }
+}
+
+// min/max, scale, codes and stores of one tile whose values are already in registers
+template <int DT, int BITS, int RNG, bool FMA, bool FULL>
+__device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, int lane,
+                                             const uint32_t (&raw)[Tile<DT, BITS>::GPW][RawRegs<DT>::N]) {
     using E = Elem<DT>;
     using T = typename E::T;
     constexpr int WPT = Tile<DT, BITS>::WPT, GPW = Tile<DT, BITS>::GPW, U = Tile<DT, BITS>::U;
-    constexpr int NR = RawRegs<DT>::N;
+    const int64_t g0 = tile * GPW;
 
-    const int lane = threadIdx.x & 31;
-    const int64_t nwarps = (int64_t)gridDim.x * (kQThreads / 32);
-    const int64_t tiles = (a.G + GPW - 1) / GPW;
-    const uint32_t key0 = (uint32_t)a.seed, key1 = (uint32_t)(a.seed >> 32);
+    // min / max of every group; lane k keeps group k's pair and computes its scale
+    float mn[GPW], sc[GPW];
+    float my_mn = 0.0f, my_mx = 0.0f;
+#pragma unroll
+    for (int k = 0; k < GPW; k++) {
+        float lo, hi;
+        group_minmax_raw<DT>(raw[k], lane, lo, hi);
+        mn[k] = lo;
+        if (lane == k) { my_mn = lo; my_mx = hi; }
+    }
+    const float my_sc = compute_scale<DT>(my_mn, my_mx, BITS);
+    if (lane < GPW && (FULL || g0 + lane < a.G)) {
+        ((T*)a.qmin)[g0 + lane] = E::from_float(my_mn);
+        store_scale<DT>(a.qscale, g0 + lane, my_sc);
+    }
+#pragma unroll
+    for (int k = 0; k < GPW; k++) sc[k] = __shfl_sync(kFull, my_sc, k);
 
-    for (int64_t tile = (int64_t)blockIdx.x * (kQThreads / 32) + (threadIdx.x >> 5); tile < tiles; tile += nwarps) {
-        const int64_t g0 = tile * GPW;
-
-        uint32_t raw[GPW][NR];
+    // codes, one row-block at a time: acc[j] collects byte (row-block, position lane*8 + j)
 #pragma unroll
-        for (int k = 0; k < GPW; k++) {
-            if (g0 + k < a.G) {
-                load_raw<DT>(a.x, a.n, g0 + k, lane, a.aligned32 != 0, raw[k]);
-            } else {
+    for (int u = 0; u < U; u++) {
+        const int64_t r = tile * U + u;
+        if (!FULL && r >= a.R) break;
+        uint32_t acc[8];
 #pragma unroll
-                for (int i = 0; i < NR; i++) raw[k][i] = 0;
-            }
-        }
-
-        // min / max of every group; lane k keeps group k's pair and computes its scale
-        float mn[GPW], sc[GPW];
-        float my_mn = 0.0f, my_mx = 0.0f;
-#pragma unroll
-        for (int k = 0; k < GPW; k++) {
-            float lo, hi;
-            group_minmax_raw<DT>(raw[k], lane, lo, hi);
-            mn[k] = lo;
-            if (lane == k) { my_mn = lo; my_mx = hi; }
-        }
-        const float my_sc = compute_scale<DT>(my_mn, my_mx, BITS);
-        if (lane < GPW && g0 + lane < a.G) {
-            ((T*)a.qmin)[g0 + lane] = E::from_float(my_mn);
-            store_scale<DT>(a.qscale, g0 + lane, my_sc);
-        }
-#pragma unroll
-        for (int k = 0; k < GPW; k++) sc[k] = __shfl_sync(kFull, my_sc, k);
-
-        // codes: acc[u][j] collects byte (row-block u, position lane*8 + j)
-        uint32_t acc[U][8];
-#pragma unroll
-        for (int u = 0; u < U; u++)
-#pragma unroll
-            for (int j = 0; j < 8; j++) acc[u][j] = 0;
+        for (int j = 0; j < 8; j++) acc[j] = 0;
 
         if (RNG == GACT_RNG_CURAND) {
             // the reference stream: one generator per packed byte (subsequence = byte index), slot ni = draw ni
+            const uint64_t gid0 = (uint64_t)r * kGroup + lane * 8;
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const uint64_t gid0 = (uint64_t)(tile * U + u) * kGroup + lane * 8;
+            for (int c = 0; c < (WPT + 3) / 4; c++) {
+                float2 nz[4][4];
 #pragma unroll
-                for (int c = 0; c < (WPT + 3) / 4; c++) {
-                    float nz[4][8];
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint64_t gid = gid0 + j;
-                        const uint4 r = philox4x32_10((uint32_t)c, 0u, (uint32_t)gid, (uint32_t)(gid >> 32), key0, key1);
-                        nz[0][j] = uniform_from_word(r.x);
-                        if (WPT > 1) nz[1][j] = uniform_from_word(r.y);
-                        if (WPT > 2) { nz[2][j] = uniform_from_word(r.z); nz[3][j] = uniform_from_word(r.w); }
+                for (int i = 0; i < 4; i++) {
+                    const uint64_t gid = gid0 + 2 * i;
+                    const uint4 ra = philox4x32_10((uint32_t)c, 0u, (uint32_t)gid, (uint32_t)(gid >> 32), a.rk);
+                    const uint4 rb = philox4x32_10((uint32_t)c, 0u, (uint32_t)(gid + 1), (uint32_t)((gid + 1) >> 32), a.rk);
+                    // cuRAND's uniform: float(word) * 2^-32 + 2^-33
+                    const float2 s2 = splat2(2.3283064365386963e-10f), o2 = splat2(1.1641532182693481e-10f);
+                    nz[0][i] = fma2(make_float2(__uint2float_rn(ra.x), __uint2float_rn(rb.x)), s2, o2);
+                    if (WPT > 1) nz[1][i] = fma2(make_float2(__uint2float_rn(ra.y), __uint2float_rn(rb.y)), s2, o2);
+                    if (WPT > 2) {
+                        nz[2][i] = fma2(make_float2(__uint2float_rn(ra.z), __uint2float_rn(rb.z)), s2, o2);
+                        nz[3][i] = fma2(make_float2(__uint2float_rn(ra.w), __uint2float_rn(rb.w)), s2, o2);
                     }
+                }
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const int ni = c * 4 + q;
-                        if (ni >= WPT) break;
-                        const int k = u * WPT + ni;
-                        if (g0 + k >= a.G) break;                  // tail row-block: absent groups leave zero bits
-                        uint32_t cb[8];
-                        codes8<DT, BITS, FMA>(raw[k], mn[k], sc[k], nz[q], cb);
+                for (int q = 0; q < 4; q++) {
+                    const int ni = c * 4 + q;
+                    if (ni >= WPT) break;
+                    const int k = u * WPT + ni;
+                    if (!FULL && g0 + k >= a.G) break;         // tail row-block: absent groups leave zero bits
+                    uint32_t cb[8];
+                    codes8<DT, BITS, FMA>(raw[k], mn[k], sc[k], nz[q], cb);
 #pragma unroll
-                        for (int j = 0; j < 8; j++) acc[u][j] |= cb[j] << (ni * BITS);
-                    }
+                    for (int j = 0; j < 8; j++) acc[j] |= cb[j] << (ni * BITS);
                 }
             }
         } else {
 #pragma unroll
-            for (int k = 0; k < GPW; k++) {
-                if (g0 + k >= a.G) break;
-                const int u = k / WPT, ni = k % WPT;
-                float nz[8];
+            for (int ni = 0; ni < WPT; ni++) {
+                const int k = u * WPT + ni;
+                if (!FULL && g0 + k >= a.G) break;
+                float2 nz[4];
                 if (RNG == GACT_RNG_FAST) {
-                    fast_noise8((uint64_t)(g0 + k) * (kGroup / 8) + lane, key0, key1, nz);
+                    fast_noise8((uint64_t)(g0 + k) * (kGroup / 8) + lane, a.rk, nz);
                 } else if (RNG == GACT_RNG_RTN) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) nz[j] = 0.5f;
+                    for (int i = 0; i < 4; i++) nz[i] = splat2(0.5f);
                 } else {
-                    const float* p = a.noise + (g0 + k) * kGroup + lane * 8;
+                    const float2* p = (const float2*)(a.noise + (g0 + k) * kGroup + lane * 8);
 #pragma unroll
-                    for (int j = 0; j < 8; j++) nz[j] = p[j];
+                    for (int i = 0; i < 4; i++) nz[i] = p[i];
                 }
                 uint32_t cb[8];
                 codes8<DT, BITS, FMA>(raw[k], mn[k], sc[k], nz, cb);
 #pragma unroll
-                for (int j = 0; j < 8; j++) acc[u][j] |= cb[j] << (ni * BITS);
+                for (int j = 0; j < 8; j++) acc[j] |= cb[j] << (ni * BITS);
             }
         }
+        // low bytes of the eight accumulators -> two words -> one 8-byte store
+        const uint32_t lo = __byte_perm(__byte_perm(acc[0], acc[1], 0x0040u), __byte_perm(acc[2], acc[3], 0x0040u), 0x5410u);
+        const uint32_t hi = __byte_perm(__byte_perm(acc[4], acc[5], 0x0040u), __byte_perm(acc[6], acc[7], 0x0040u), 0x5410u);
+        st_stream_u2(a.packed + r * kGroup + lane * 8, make_uint2(lo, hi));
+    }
+}
 
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int64_t r = tile * U + u;
-            if (r >= a.R) break;
-            // low bytes of the eight accumulators -> two words
-            const uint32_t lo = __byte_perm(__byte_perm(acc[u][0], acc[u][1], 0x0040u), __byte_perm(acc[u][2], acc[u][3], 0x0040u), 0x5410u);
-            const uint32_t hi = __byte_perm(__byte_perm(acc[u][4], acc[u][5], 0x0040u), __byte_perm(acc[u][6], acc[u][7], 0x0040u), 0x5410u);
-            st_stream_u2(a.packed + r * kGroup + lane * 8, make_uint2(lo, hi));
+#ifndef GACT_QMINB
+#define GACT_QMINB 3
+#endif
+
+template <int DT, int BITS, int RNG, bool FMA>
+__global__ void __launch_bounds__(kQThreads, GACT_QMINB) quantize_kernel(const __grid_constant__ QuantArgs a) {
+    constexpr int GPW = Tile<DT, BITS>::GPW, NR = RawRegs<DT>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = (int64_t)gridDim.x * (kQThreads / 32);
+    const int64_t tiles = (a.G + GPW - 1) / GPW;
+    const int64_t full_tiles = a.n / (GPW * kGroup);            // tiles whose groups all exist and are complete
+    for (int64_t tile = (int64_t)blockIdx.x * (kQThreads / 32) + (threadIdx.x >> 5); tile < tiles; tile += nwarps) {
+        uint32_t raw[GPW][NR];
+        if (tile < full_tiles) {
+            load_tile<DT, BITS, true>(a, tile, lane, raw);
+            process_tile<DT, BITS, RNG, FMA, true>(a, tile, lane, raw);
+        } else {
+            load_tile<DT, BITS, false>(a, tile, lane, raw);
+            process_tile<DT, BITS, RNG, FMA, false>(a, tile, lane, raw);
         }
     }
 }
 
 template <int DT, int BITS, int RNG, bool FMA>
 static int launch_quantize(const QuantArgs& a, cudaStream_t s) {
+    // one resident wave: as many CTAs as fit on the 148 SMs (the kernel strides over the tiles)
+    static int resident = 0;
+    if (resident == 0) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_kernel<DT, BITS, RNG, FMA>, kQThreads, 0) != cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        resident = per_sm * kSMs;
+    }
     const int64_t tiles = (a.G + Tile<DT, BITS>::GPW - 1) / Tile<DT, BITS>::GPW;
     const int64_t want = (tiles + kQThreads / 32 - 1) / (kQThreads / 32);
-    const int64_t cap = (int64_t)kSMs * 16;
-    const int blocks = (int)(want < cap ? want : cap);
+    const int blocks = (int)(want < resident ? want : resident);
     quantize_kernel<DT, BITS, RNG, FMA><<<blocks, kQThreads, 0, s>>>(a);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }
@@ -298,7 +331,7 @@ extern "C" int gact_quantize(const void* x, int dtype, int64_t n, int bits, uint
     if (rng_mode < GACT_RNG_CURAND || rng_mode > GACT_RNG_EXTERNAL) return GACT_ERR_MODE;
     if (n == 0) return GACT_OK;
     if (!x || !packed || !qmin || !qscale) return GACT_ERR_NULL;
-    if (rng_mode == GACT_RNG_EXTERNAL && !noise) return GACT_ERR_MODE;
+    if (rng_mode == GACT_RNG_EXTERNAL && (!noise || misaligned(noise, 8))) return GACT_ERR_MODE;
     if (misaligned(x, 16) || misaligned(packed, 16) || misaligned(qmin, dtype == GACT_F32 ? 4 : 2) ||
         misaligned(qscale, dtype == GACT_F16 ? 2 : 4))
         return GACT_ERR_ALIGN;
@@ -307,6 +340,7 @@ extern "C" int gact_quantize(const void* x, int dtype, int64_t n, int bits, uint
     a.R = (a.G + 8 / bits - 1) / (8 / bits);
     a.seed = seed; a.noise = noise; a.packed = (uint8_t*)packed; a.qmin = qmin; a.qscale = qscale;
     a.aligned32 = misaligned(x, 32) ? 0 : 1;
+    a.rk = philox_round_keys(seed);
     cudaStream_t s = (cudaStream_t)stream;
     switch (dtype) {
     case GACT_F32: return dispatch_bits<GACT_F32>(a, bits, rng_mode, fma_mode, s);
