@@ -48,6 +48,11 @@ __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_
 
 // Two fp32 operations per instruction (sm_100 add/fma .f32x2): each half is an ordinary IEEE
 // round-to-nearest operation, so results are bit-identical to the scalar forms.
+#ifdef GACT_NO_F32X2
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y)); }
+#else
 __device__ __forceinline__ float2 add2(float2 a, float2 b) {
     float2 d;
     asm("{ .reg .b64 ra, rb, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; add.rn.f32x2 rd, ra, rb; mov.b64 {%0,%1}, rd; }"
@@ -67,6 +72,7 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
         : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
     return d;
 }
+#endif
 __device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
 
 // cuRAND's curand_uniform mapping of one 32-bit word to (0, 1]: float(w) * 2^-32 + 2^-33 in fp32.

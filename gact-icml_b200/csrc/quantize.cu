@@ -29,6 +29,7 @@ struct QuantArgs {
     void* qmin;
     void* qscale;
     int aligned32;
+    int64_t tile_begin;      // first tile of the plain kernel (tiles before it belong to the bulk-copy kernel)
     PhiloxKeys rk;
 };
 
@@ -41,17 +42,20 @@ template <int DT, int BITS> struct Tile {
     static constexpr int U = GPW / WPT;
 };
 
-// noise of the FAST arrangement for the 8 elements [8*block, 8*block+8): one Philox4x32-10 call, counter
-// (block_lo, block_hi, 0, "FAST"), 16 bits per element, noise = (h + 0.5) * 2^-16
-__device__ __forceinline__ void fast_noise8(uint64_t block, const PhiloxKeys& rk, float2 (&nz)[4]) {
+// noise of the FAST arrangement: one Philox4x32-10 call, counter (block_lo, block_hi, 0, "FAST"), gives 16
+// bytes = 8 bits for each of this lane's 8 elements of an even group (bytes 0..7) and of the following odd group
+// (bytes 8..15); noise = (byte + 0.5) / 256.  The bytes go to float on the conversion unit.
+__device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& rk, float2 (&even)[4], float2 (&odd)[4]) {
     const uint4 r = philox4x32_10((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    const float2 s2 = splat2(0.00390625f), o2 = splat2(0.001953125f);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        // both halfwords to float on the conversion unit (no shift / mask), then (h + 0.5) * 2^-16, exact
-        float lo, hi;
-        asm("{ .reg .b16 l, h; mov.b32 {l, h}, %2; cvt.rn.f32.u16 %0, l; cvt.rn.f32.u16 %1, h; }" : "=f"(lo), "=f"(hi) : "r"(w[i]));
-        nz[i] = fma2(make_float2(lo, hi), splat2(1.52587890625e-05f), splat2(7.62939453125e-06f));
+        const float b0 = __uint2float_rn(w[i] & 0xffu), b1 = __uint2float_rn((w[i] >> 8) & 0xffu);
+        const float b2 = __uint2float_rn((w[i] >> 16) & 0xffu), b3 = __uint2float_rn(w[i] >> 24);
+        float2 (&dst)[4] = (i < 2) ? even : odd;
+        dst[(2 * i) & 3] = fma2(make_float2(b0, b1), s2, o2);
+        dst[(2 * i + 1) & 3] = fma2(make_float2(b2, b3), s2, o2);
     }
 }
 
@@ -151,6 +155,7 @@ __device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, i
     for (int k = 0; k < GPW; k++) sc[k] = __shfl_sync(kFull, my_sc, k);
 
     // codes, one row-block at a time: acc[j] collects byte (row-block, position lane*8 + j)
+    float2 nz_odd[4];            // FAST: noise of an odd group, produced together with the even group before it
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const int64_t r = tile * U + u;
@@ -193,12 +198,18 @@ __device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, i
             }
         } else {
 #pragma unroll
+#pragma unroll
             for (int ni = 0; ni < WPT; ni++) {
                 const int k = u * WPT + ni;
                 if (!FULL && g0 + k >= a.G) break;
                 float2 nz[4];
                 if (RNG == GACT_RNG_FAST) {
-                    fast_noise8((uint64_t)(g0 + k) * (kGroup / 8) + lane, a.rk, nz);
+                    if ((k & 1) == 0) {
+                        fast_noise16((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) nz[i] = nz_odd[i];
+                    }
                 } else if (RNG == GACT_RNG_RTN) {
 #pragma unroll
                     for (int i = 0; i < 4; i++) nz[i] = splat2(0.5f);
@@ -231,7 +242,7 @@ __global__ void __launch_bounds__(kQThreads, GACT_QMINB) quantize_kernel(const _
     const int64_t nwarps = (int64_t)gridDim.x * (kQThreads / 32);
     const int64_t tiles = (a.G + GPW - 1) / GPW;
     const int64_t full_tiles = a.n / (GPW * kGroup);            // tiles whose groups all exist and are complete
-    for (int64_t tile = (int64_t)blockIdx.x * (kQThreads / 32) + (threadIdx.x >> 5); tile < tiles; tile += nwarps) {
+    for (int64_t tile = a.tile_begin + (int64_t)blockIdx.x * (kQThreads / 32) + (threadIdx.x >> 5); tile < tiles; tile += nwarps) {
         uint32_t raw[GPW][NR];
         if (tile < full_tiles) {
             load_tile<DT, BITS, true>(a, tile, lane, raw);
@@ -243,21 +254,175 @@ __global__ void __launch_bounds__(kQThreads, GACT_QMINB) quantize_kernel(const _
     }
 }
 
-template <int DT, int BITS, int RNG, bool FMA>
-static int launch_quantize(const QuantArgs& a, cudaStream_t s) {
-    // one resident wave: as many CTAs as fit on the 148 SMs (the kernel strides over the tiles)
-    static int resident = 0;
-    if (resident == 0) {
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_kernel<DT, BITS, RNG, FMA>, kQThreads, 0) != cudaSuccess || per_sm < 1)
-            per_sm = 1;
-        resident = per_sm * kSMs;
+// ---------------------------------------------------------------------------------------------------
+// Bulk-copy pipeline (the main path).  Persistent CTAs of 8 consumer warps + 1 producer warp.  The producer's
+// elected lane streams chunks of the input (one tile per consumer warp: 32 KB, or 64 KB for 1-bit fp32) into a
+// 3-stage (2 for the 64 KB chunks) shared-memory ring with cp.async.bulk (the TMA
+// engine, plain 1-D copies of this GPU's own memory, no multicast); an mbarrier per stage counts the bytes in.
+// Each consumer warp takes its tile of the chunk out of shared memory (16- or 32-byte reads, conflict free),
+// releases the stage, and runs the same tile routine as the plain kernel.  64 KB per CTA are in flight
+// whatever the warps are doing, so HBM latency is hidden without holding loads in registers.
+// Every wait is bounded: a wait that runs out sets g_pipeline_error and the CTA winds down.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kPipeWarps = 8;                         // consumer warps
+constexpr int kPipeThreads = (kPipeWarps + 1) * 32;
+constexpr uint32_t kWaitLimit = 1u << 20;
+#ifndef GACT_PIPE_STAGES
+#define GACT_PIPE_STAGES 3
+#endif
+#ifndef GACT_PIPE_MINB
+#define GACT_PIPE_MINB 2
+#endif
+template <int DT, int BITS> struct Pipe {
+    static constexpr int kChunkBytes = kPipeWarps * Tile<DT, BITS>::GPW * kGroup * Elem<DT>::kBytes;
+    static constexpr int kStages = kChunkBytes <= 32 * 1024 ? GACT_PIPE_STAGES : 2;
+};
+
+__device__ int g_pipeline_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// true once the phase with the given parity has completed; gives up after kWaitLimit polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
     }
-    const int64_t tiles = (a.G + Tile<DT, BITS>::GPW - 1) / Tile<DT, BITS>::GPW;
-    const int64_t want = (tiles + kQThreads / 32 - 1) / (kQThreads / 32);
-    const int blocks = (int)(want < resident ? want : resident);
-    quantize_kernel<DT, BITS, RNG, FMA><<<blocks, kQThreads, 0, s>>>(a);
-    return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+    return false;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+template <int DT, int BITS, int RNG, bool FMA>
+__global__ void __launch_bounds__(kPipeThreads, GACT_PIPE_MINB) quantize_pipe_kernel(const __grid_constant__ QuantArgs a, int64_t nchunks) {
+    constexpr int GPW = Tile<DT, BITS>::GPW, NR = RawRegs<DT>::N;
+    constexpr int kChunkBytes = Pipe<DT, BITS>::kChunkBytes, kPipeStages = Pipe<DT, BITS>::kStages;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t bars[2 * kPipeStages];       // [0..S) full, [S..2S) empty
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars), ring = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < kPipeStages; s++) {
+            mbar_init(bar0 + 8 * s, 1);                           // full: the producer's expect_tx arrival
+            mbar_init(bar0 + 8 * (kPipeStages + s), kPipeWarps);  // empty: one arrival per consumer warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kPipeWarps) {
+        // ---- producer ----
+        if (lane == 0) {
+            int64_t issued = 0;
+            bool ok = true;
+            for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x, ++issued) {
+                const int s = (int)(issued % kPipeStages);
+                if (issued >= kPipeStages && !mbar_wait(bar0 + 8 * (kPipeStages + s), (uint32_t)((issued / kPipeStages - 1) & 1))) {
+                    ok = false;
+                    break;
+                }
+                mbar_expect_tx(bar0 + 8 * s, kChunkBytes);
+                bulk_load(ring + s * kChunkBytes, (const unsigned char*)a.x + c * kChunkBytes, kChunkBytes, bar0 + 8 * s);
+            }
+            if (!ok) {
+                atomicExch(&g_pipeline_error, 1);
+                // do not leave while copies into this CTA's shared memory may still be in flight
+                const int64_t first = issued > kPipeStages ? issued - kPipeStages : 0;
+                for (int64_t i = first; i < issued; ++i)
+                    mbar_wait(bar0 + 8 * (int)(i % kPipeStages), (uint32_t)((i / kPipeStages) & 1));
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ----
+    int64_t done = 0;
+    for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x, ++done) {
+        const int s = (int)(done % kPipeStages);
+        // all lanes poll; the verdict is taken jointly so that the warp never splits
+        if (!__all_sync(kFull, mbar_wait(bar0 + 8 * s, (uint32_t)((done / kPipeStages) & 1)))) {
+            if (lane == 0) atomicExch(&g_pipeline_error, 2);
+            return;
+        }
+        uint32_t raw[GPW][NR];
+        const unsigned char* src = smem + s * kChunkBytes + warp * (GPW * kGroup * Elem<DT>::kBytes) + lane * (8 * Elem<DT>::kBytes);
+#pragma unroll
+        for (int k = 0; k < GPW; k++) {
+            const uint4* p = (const uint4*)(src + k * (kGroup * Elem<DT>::kBytes));
+            if constexpr (DT == GACT_F32) {
+                const uint4 v0 = p[0], v1 = p[1];
+                raw[k][0] = v0.x; raw[k][1] = v0.y; raw[k][2] = v0.z; raw[k][3] = v0.w;
+                raw[k][4] = v1.x; raw[k][5] = v1.y; raw[k][6] = v1.z; raw[k][7] = v1.w;
+            } else {
+                const uint4 v0 = p[0];
+                raw[k][0] = v0.x; raw[k][1] = v0.y; raw[k][2] = v0.z; raw[k][3] = v0.w;
+            }
+        }
+        __threadfence_block();                                       // this lane's reads of the stage are done
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8 * (kPipeStages + s));    // the stage may be refilled
+        process_tile<DT, BITS, RNG, FMA, true>(a, c * kPipeWarps + warp, lane, raw);
+    }
+}
+
+template <int DT, int BITS, int RNG, bool FMA>
+static int launch_quantize(const QuantArgs& args, cudaStream_t s) {
+    constexpr int GPW = Tile<DT, BITS>::GPW;
+    constexpr int kChunkBytes = Pipe<DT, BITS>::kChunkBytes, kPipeStages = Pipe<DT, BITS>::kStages;
+    QuantArgs a = args;
+    // ---- bulk-copy pipeline over the whole 32 KB chunks (needs 16-byte aligned input, which the ABI demands)
+    const int64_t nchunks = a.n / (kChunkBytes / Elem<DT>::kBytes);
+    static int pipe_ready = 0;          // 0 = not set up, 1 = usable, -1 = shared memory opt-in refused
+    if (pipe_ready == 0) {
+        pipe_ready = cudaFuncSetAttribute(quantize_pipe_kernel<DT, BITS, RNG, FMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kPipeStages * kChunkBytes) == cudaSuccess ? 1 : -1;
+    }
+    a.tile_begin = 0;
+    if (nchunks > 0 && pipe_ready == 1) {
+        static int pipe_resident = 0;
+        if (pipe_resident == 0) {
+            int per_sm = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_pipe_kernel<DT, BITS, RNG, FMA>, kPipeThreads,
+                                                              kPipeStages * kChunkBytes) != cudaSuccess || per_sm < 1)
+                per_sm = 1;
+            pipe_resident = per_sm * kSMs;
+        }
+        const int64_t cap = pipe_resident;
+        const int blocks = (int)(nchunks < cap ? nchunks : cap);
+        quantize_pipe_kernel<DT, BITS, RNG, FMA><<<blocks, kPipeThreads, kPipeStages * kChunkBytes, s>>>(a, nchunks);
+        if (cudaGetLastError() != cudaSuccess) return GACT_ERR_LAUNCH;
+        a.tile_begin = nchunks * kPipeWarps;
+    }
+    // ---- plain kernel for what is left (less than one chunk, or everything if the pipeline is unavailable)
+    const int64_t tiles = (a.G + GPW - 1) / GPW - a.tile_begin;
+    if (tiles > 0) {
+        static int resident = 0;
+        if (resident == 0) {
+            int per_sm = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_kernel<DT, BITS, RNG, FMA>, kQThreads, 0) != cudaSuccess || per_sm < 1)
+                per_sm = 1;
+            resident = per_sm * kSMs;
+        }
+        const int64_t want = (tiles + kQThreads / 32 - 1) / (kQThreads / 32);
+        const int blocks = (int)(want < resident ? want : resident);
+        quantize_kernel<DT, BITS, RNG, FMA><<<blocks, kQThreads, 0, s>>>(a);
+        if (cudaGetLastError() != cudaSuccess) return GACT_ERR_LAUNCH;
+    }
+    return GACT_OK;
 }
 
 template <int DT, int BITS>
@@ -341,12 +506,19 @@ extern "C" int gact_quantize(const void* x, int dtype, int64_t n, int bits, uint
     a.seed = seed; a.noise = noise; a.packed = (uint8_t*)packed; a.qmin = qmin; a.qscale = qscale;
     a.aligned32 = misaligned(x, 32) ? 0 : 1;
     a.rk = philox_round_keys(seed);
+    a.tile_begin = 0;
     cudaStream_t s = (cudaStream_t)stream;
     switch (dtype) {
     case GACT_F32: return dispatch_bits<GACT_F32>(a, bits, rng_mode, fma_mode, s);
     case GACT_F16: return dispatch_bits<GACT_F16>(a, bits, rng_mode, fma_mode, s);
     default: return dispatch_bits<GACT_BF16>(a, bits, rng_mode, fma_mode, s);
     }
+}
+
+extern "C" int gact_pipeline_error(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_pipeline_error, sizeof(int)) != cudaSuccess) return -1;
+    return v;
 }
 
 extern "C" int gact_minimax(const void* x, int dtype, int64_t n, void* mn, void* mx, void* stream) {

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "gact_error_string": ([_i], C.c_char_p),
     "gact_packed_bytes": ([_i64, _i], _i64),
     "gact_quantize": ([_vp, _i, _i64, _i, _u64, _i, _vp, _i, _vp, _vp, _vp, _vp], _i),
+    "gact_pipeline_error": ([], _i),
     "gact_dequantize": ([_vp, _vp, _vp, _i, _i64, _i, _vp, _vp], _i),
     "gact_minimax": ([_vp, _i, _i64, _vp, _vp, _vp], _i),
     "gact_mask_words": ([_i64], _i64),
@@ -71,3 +72,22 @@ def require_cuda(t: torch.Tensor, name: str) -> None:
 
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(t: torch.Tensor):
+    """Context that makes the tensor's device current for the duration of a library call.  The hooks almost
+    always run with the right device already current, in which case this costs one comparison."""
+    if t.device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(t.device)

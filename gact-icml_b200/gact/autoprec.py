@@ -56,6 +56,7 @@ class AutoPrecision:
 
         self._flat = [None, None]     # gradient snapshots of the first two probe passes
         self._scratch = None
+        self._device = None           # device of the parameter gradients (set by the first probe)
         self.last_status = 0          # status of the last greedy allocation (0 = budget met)
 
     def init_from_dims(self):
@@ -134,15 +135,18 @@ class AutoPrecision:
         if self._scratch is None or self._scratch.device != dev:
             self._scratch = torch.empty(nv.lib.gact_sq_diffs3_scratch_bytes(), dtype=torch.uint8, device=dev)
         direct = all(g.dtype == torch.float32 and g.is_contiguous() for g in grads)
-        with torch.cuda.device(dev):
+        with nv.device_guard(flat0):
             if direct:
                 offs = np.cumsum([0] + [g.numel() for g in grads[:-1]])
                 table = torch.tensor([[g.data_ptr() for g in grads], offs.tolist(), [g.numel() for g in grads]],
-                                     dtype=torch.int64).pin_memory().to(dev, non_blocking=True)
+                                     dtype=torch.int64)
+                if dev.type == 'cuda':
+                    table = table.pin_memory().to(dev, non_blocking=True)
                 st = nv.lib.gact_sq_diffs3(flat0.data_ptr(), flat1.data_ptr(), None, flat0.numel(),
                                            table[0].data_ptr(), table[1].data_ptr(), table[2].data_ptr(), len(grads),
                                            self._scratch.data_ptr(), out3.data_ptr(), nv.stream_ptr())
-                table.record_stream(torch.cuda.current_stream())
+                if dev.type == 'cuda':
+                    table.record_stream(torch.cuda.current_stream())
             else:
                 flat2 = torch.cat([g.reshape(-1).float() for g in grads])
                 st = nv.lib.gact_sq_diffs3(flat0.data_ptr(), flat1.data_ptr(), flat2.data_ptr(), flat0.numel(),
@@ -162,7 +166,7 @@ class AutoPrecision:
             self._run_backprop(backprop)
             grads = self._grads()
             if d3 is None:
-                dev = grads[0].device
+                dev = self._device = grads[0].device
                 d3 = torch.zeros((L, 3), dtype=torch.float64, device=dev)
             flat0 = self._snapshot(0, grads)
             q.iterate()
@@ -189,7 +193,7 @@ class AutoPrecision:
             # the squared distance of the averaged gradient is the sum of the local ones over W^2.
             scale = 1.0 / (W * W) if config.dp_probe == "local" else 1.0 / W
         C_dev = torch.empty(L, dtype=torch.float32, device=dev)
-        with torch.cuda.device(dev):
+        with nv.device_guard(C_dev):
             st = nv.lib.gact_sensitivity(d3.data_ptr(), scale, C_dev.data_ptr(), L, nv.stream_ptr())
         nv.check(st, "gact_sensitivity")
         for l, c in zip(tids, C_dev.tolist()):            # the only host synchronisation of the probe
@@ -248,11 +252,11 @@ class AutoPrecision:
         L = len(l_list)
         if L == 0:
             return
-        dev = torch.device("cuda", torch.cuda.current_device())
+        dev = self._device if self._device is not None else next(self.model.parameters()).device
         dims_dev = torch.tensor([self.dims[l] for l in l_list], dtype=torch.int64).to(dev)
         C_dev = torch.tensor([self.C[l] for l in l_list], dtype=torch.float32).to(dev)
         bits_dev = torch.full((L + 1,), self.max_bits, dtype=torch.int32, device=dev)   # [L] = status
-        with torch.cuda.device(dev):
+        with nv.device_guard(bits_dev):
             st = nv.lib.gact_calc_precision(bits_dev.data_ptr(), C_dev.data_ptr(), dims_dev.data_ptr(), L,
                                             float(self.total_bits), bits_dev[L:].data_ptr(), nv.stream_ptr())
         nv.check(st, "gact_calc_precision")

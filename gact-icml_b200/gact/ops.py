@@ -42,7 +42,7 @@ def quantize_pack(input, q_bit, seed, rng_mode=None, noise=None, fma=None):
         if noise.numel() != G * nv.GROUP:
             raise ValueError("noise must have G*256 elements")
         noise_ptr = noise.data_ptr()
-    with torch.cuda.device(x.device):
+    with nv.device_guard(x):
         st = nv.lib.gact_quantize(x.data_ptr(), nv.DTYPE_CODE[x.dtype], n, q_bit, int(seed) & 0xFFFFFFFFFFFFFFFF, mode,
                                   noise_ptr, int(config.fma if fma is None else fma), q_input.data_ptr(),
                                   q_min.data_ptr(), q_scale.data_ptr(), nv.stream_ptr())
@@ -79,7 +79,7 @@ def dequantize_and_unpack(data, shape, q_bit, scale, mn):
     nv.require_cuda(data, "data")
     n = _numel(shape)
     out = torch.empty(tuple(int(s) for s in shape), dtype=mn.dtype, device=data.device)
-    with torch.cuda.device(data.device):
+    with nv.device_guard(data):
         st = nv.lib.gact_dequantize(data.data_ptr(), mn.data_ptr(), scale.data_ptr(), nv.DTYPE_CODE[mn.dtype], n, q_bit,
                                     out.data_ptr(), nv.stream_ptr())
     nv.check(st, "gact_dequantize")
@@ -96,7 +96,7 @@ def op_quantize_mask(input, flag=None):
     x = input.contiguous()
     n = x.numel()
     words = torch.empty(nv.lib.gact_mask_words(n), dtype=torch.int32, device=x.device)
-    with torch.cuda.device(x.device):
+    with nv.device_guard(x):
         st = nv.lib.gact_mask_pack(x.data_ptr(), n, words.data_ptr(), None if flag is None else flag.data_ptr(),
                                    nv.stream_ptr())
     nv.check(st, "gact_mask_pack")
@@ -108,7 +108,7 @@ def op_dequantize_mask(input, dtype=torch.uint8):
     q_mask, input_shape = input
     n = _numel(input_shape)
     out = torch.empty(tuple(int(s) for s in input_shape), dtype=torch.uint8, device=q_mask.device)
-    with torch.cuda.device(q_mask.device):
+    with nv.device_guard(q_mask):
         st = nv.lib.gact_mask_unpack(q_mask.data_ptr(), n, out.data_ptr(), nv.stream_ptr())
     nv.check(st, "gact_mask_unpack")
     return out if dtype == torch.uint8 else out.view(dtype)
@@ -138,7 +138,7 @@ def minimax(data):
     x = data.contiguous()
     mn = torch.empty(x.shape[0], dtype=x.dtype, device=x.device)
     mx = torch.empty_like(mn)
-    with torch.cuda.device(x.device):
+    with nv.device_guard(x):
         st = nv.lib.gact_minimax(x.data_ptr(), nv.DTYPE_CODE[x.dtype], x.numel(), mn.data_ptr(), mx.data_ptr(), nv.stream_ptr())
     nv.check(st, "gact_minimax")
     return mn, mx

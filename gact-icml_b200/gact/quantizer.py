@@ -50,6 +50,11 @@ class Quantizer:
         for _, v in pairs:
             self.unrelated_tensors.add(v.data_ptr())
 
+    @staticmethod
+    def _on_device(t):
+        """Only tensors that live on a GPU are compressed; anything else passes through untouched."""
+        return t.is_cuda
+
     # returns (should_be_quantized, is_dropout_mask)
     def check_quantize(self, input_tensor):
         # parameters are not compressed
@@ -58,10 +63,10 @@ class Quantizer:
         # 0/1 byte tensors (dropout masks) take the 1-bit path
         if input_tensor.numel() > 0:
             if input_tensor.dtype == torch.bool and config.pack_bool_masks:
-                return input_tensor.is_cuda, True
+                return self._on_device(input_tensor), True
             if input_tensor.dtype == torch.uint8:
                 # decided after packing, from the flag the pack kernel raises (see quantize)
-                return input_tensor.is_cuda, True
+                return self._on_device(input_tensor), True
         dtypes = (torch.float32, torch.float16, torch.bfloat16) if config.quantize_bf16 \
             else (torch.float32, torch.float16)
         if input_tensor.dtype not in dtypes:
@@ -72,7 +77,7 @@ class Quantizer:
         # 2-D, 3-D and 4-D tensors only, as in the reference
         if input_tensor.dim() not in (2, 3, 4):
             return False, False
-        if not input_tensor.is_cuda:
+        if not self._on_device(input_tensor):
             return False, False
         return True, False
 

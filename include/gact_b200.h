@@ -33,7 +33,7 @@ enum { GACT_F32 = 0, GACT_F16 = 1, GACT_BF16 = 2 };
 /* where the rounding noise comes from */
 enum {
     GACT_RNG_CURAND = 0,   /* the reference's stream: curand_init(seed, byte index, 0) + curand_uniform per slot */
-    GACT_RNG_FAST = 1,     /* Philox4x32-10 as well, but one call feeds 8 elements with 16 bits each */
+    GACT_RNG_FAST = 1,     /* Philox4x32-10 as well, but one call feeds 16 elements with 8 bits each */
     GACT_RNG_RTN = 2,      /* noise = 0.5 everywhere: round to nearest */
     GACT_RNG_EXTERNAL = 3  /* noise read from a caller-supplied fp32 array (G*256 values in [0,1]) */
 };
@@ -75,6 +75,13 @@ int64_t gact_packed_bytes(int64_t n, int bits);
  */
 int gact_quantize(const void* x, int dtype, int64_t n, int bits, uint64_t seed, int rng_mode,
                   const float* noise, int fma_mode, void* packed, void* qmin, void* qscale, void* stream);
+
+/*
+ * 0 while every bounded wait inside the bulk-copy pipeline of gact_quantize has been satisfied; non-zero once a
+ * wait ran out (the kernel then winds down instead of spinning).  Synchronises with the device; for tests and
+ * diagnostics.  -1 if the value could not be read.
+ */
+int gact_pipeline_error(void);
 
 /*
  * Unpack + dequantize: out[i] = T(T(code)/scale) + min for the first n elements (bf16: fp32 divide and add,

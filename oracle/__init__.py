@@ -65,6 +65,9 @@ def lib() -> ctypes.CDLL:
         L.oracle_half_to_float.restype = c.c_float
         L.oracle_float_to_bf16.argtypes = [c.c_float]
         L.oracle_float_to_bf16.restype = c.c_uint16
+        L.oracle_check_half_reciprocal.restype = c.c_int64
+        L.oracle_check_markstein.argtypes = [c.c_uint32, c.c_int]
+        L.oracle_check_markstein.restype = c.c_int64
         _lib = L
     return _lib
 

@@ -460,22 +460,67 @@ int oracle_sq_diffs3(const float *g0, const float *g1, const float *g2, int64_t 
 }
 
 /* ------------------------------------------------------------------------------------------------
- * RNG_FAST (no counterpart in the reference): one Philox4x32-10 call feeds 8 consecutive elements of the
- * zero-padded tensor with 16 bits of noise each.  Block j = elem div 8 uses counter (j_lo, j_hi, 0,
- * 0x46415354 "FAST") and key (seed_lo, seed_hi); element e = elem mod 8 takes halfword (e mod 2) of word
- * (e div 2); noise = (h + 0.5) * 2^-16, exact in fp32, in (0, 1).
+ * RNG_FAST (no counterpart in the reference): one Philox4x32-10 call feeds 16 elements with 8 bits of noise
+ * each - the 8 elements d..d+7 (d a multiple of 8) of an even group g and the same 8 positions of group g+1.
+ * Block index j = (g div 2) * 32 + (d div 8), counter (j_lo, j_hi, 0, 0x46415354 "FAST"), key (seed_lo,
+ * seed_hi); element (g, d) takes byte (g mod 2) * 8 + (d mod 8) of the 16 output bytes (word = byte div 4,
+ * little endian); noise = (byte + 0.5) / 256, exact in fp32, in (0, 1).
  * ---------------------------------------------------------------------------------------------- */
 static float fast_noise(uint64_t seed, int64_t elem) {
-    uint64_t j = (uint64_t)elem >> 3;
-    int e = (int)(elem & 7);
+    const int64_t g = elem / GROUP;
+    const int d = (int)(elem % GROUP);
+    uint64_t j = (uint64_t)(g >> 1) * 32u + (uint64_t)(d >> 3);
+    int e = (int)((g & 1) * 8 + (d & 7));
     uint32_t ctr[4] = { (uint32_t)j, (uint32_t)(j >> 32), 0u, 0x46415354u };
     uint32_t key[2] = { (uint32_t)seed, (uint32_t)(seed >> 32) };
     uint32_t out[4];
     oracle_philox4x32_10(ctr, key, out);
-    uint32_t h = (out[e >> 1] >> ((e & 1) * 16)) & 0xffffu;
-    return ((float)h + 0.5f) * 1.52587890625e-05f;
+    uint32_t b = (out[e >> 2] >> ((e & 3) * 8)) & 0xffu;
+    return ((float)b + 0.5f) * 0.00390625f;
 }
 float oracle_fast_noise(uint64_t seed, int64_t elem) { return fast_noise(seed, elem); }
+
+
+/* ------------------------------------------------------------------------------------------------
+ * Identities the division-free dequantize kernel rests on, checked by brute force (CPU tests call these).
+ * (A) fp16: round_h(fl32(c * fl32(1/s))) == round_h(fl32(c / s)) for every half-precision bit pattern s and
+ *     every code c in 0..255.  Returns the number of mismatches (NaN results count as equal).
+ * (B) fp32: with r = fl32(1/s), q0 = fl32(c*r), e = fma(-q0, s, c), q = fma(e, r, q0) is the correctly rounded
+ *     c/s.  Checked for every `stride`-th significand of s, binades 2^-60..2^59 every `bstep`-th, c in 1..255.
+ * ---------------------------------------------------------------------------------------------- */
+int64_t oracle_check_half_reciprocal(void) {
+    int64_t bad = 0;
+    for (uint32_t hs = 0; hs < 65536; hs++) {
+        const float s = half_to_float((uint16_t)hs);
+        const float r = 1.0f / s;
+        for (int c = 0; c < 256; c++) {
+            const float cf = (float)c;
+            const uint16_t a = float_to_half(cf / s), b = float_to_half(cf * r);
+            if ((a & 0x7fff) > 0x7c00 && (b & 0x7fff) > 0x7c00) continue;
+            if (a != b) bad++;
+        }
+    }
+    return bad;
+}
+
+int64_t oracle_check_markstein(uint32_t stride, int bstep) {
+    int64_t bad = 0;
+#pragma omp parallel for reduction(+:bad) schedule(static)
+    for (int64_t m = 0; m < (1 << 23); m += stride) {
+        for (int ex = 127 - 60; ex < 127 + 60; ex += bstep) {
+            const float s = u2f(((uint32_t)ex << 23) | (uint32_t)m);
+            const float r = 1.0f / s;
+            for (int c = 1; c < 256; c++) {
+                const float cf = (float)c;
+                const float q0 = cf * r;
+                const float e = fmaf(-q0, s, cf);
+                const float q = fmaf(e, r, q0);
+                if (f2u(q) != f2u(cf / s)) bad++;
+            }
+        }
+    }
+    return bad;
+}
 
 #ifdef _OPENMP
 #include <omp.h>

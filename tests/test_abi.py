@@ -1,0 +1,81 @@
+"""The C-ABI library loads and exports every symbol include/gact_b200.h declares; argument validation that needs
+no GPU answers with the documented status codes.  No kernel is launched here."""
+import ctypes
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_functions():
+    text = (ROOT / "include" / "gact_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b(gact_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for must in ("gact_quantize", "gact_dequantize", "gact_minimax", "gact_mask_pack", "gact_mask_unpack", "gact_sq_diffs3",
+                 "gact_sensitivity", "gact_calc_precision", "gact_packed_bytes", "gact_mask_words", "gact_error_string", "gact_version"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from gact import _native as nv
+    lib = ctypes.CDLL(str(nv.LIB_PATH))
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in include/gact_b200.h but not exported"
+    # and the binding covers them all
+    for name in declared_functions():
+        assert name in nv._SIGNATURES, f"{name} has no ctypes signature in gact/_native.py"
+
+
+def test_host_only_entry_points():
+    from gact import _native as nv
+    L = nv.lib
+    assert L.gact_version() >= 100
+    assert L.gact_packed_bytes(3145728, 2) == 786432                   # config 1: 12 288 groups -> 3 072 row-blocks
+    assert L.gact_packed_bytes(102760448, 1) == 12845056 and L.gact_packed_bytes(102760448, 8) == 102760448
+    assert L.gact_packed_bytes(1, 4) == 256 and L.gact_packed_bytes(0, 4) == 0
+    assert L.gact_packed_bytes(100, 3) == -1 and L.gact_packed_bytes(-5, 2) == -1
+    assert L.gact_mask_words(1) == 16 and L.gact_mask_words(512) == 16 and L.gact_mask_words(513) == 32
+    assert L.gact_sq_diffs3_scratch_bytes() > 0
+    assert L.gact_error_string(0) == b"ok" and b"bits" in L.gact_error_string(1)
+
+
+def test_argument_validation_without_a_gpu():
+    """These return before any CUDA call is made."""
+    from gact import _native as nv
+    f = nv.lib.gact_quantize
+    buf = ctypes.create_string_buffer(4096 + 64)
+    p = (ctypes.addressof(buf) + 63) & ~63
+    assert f(p, 0, 512, 3, 0, 0, None, 1, p, p, p, None) == 1            # bits
+    assert f(p, 9, 512, 2, 0, 0, None, 1, p, p, p, None) == 2            # dtype
+    assert f(None, 0, 512, 2, 0, 0, None, 1, p, p, p, None) == 3         # null pointer
+    assert f(p + 4, 0, 100, 2, 0, 0, None, 1, p, p, p, None) == 4        # alignment
+    assert f(p, 0, -1, 2, 0, 0, None, 1, p, p, p, None) == 5             # size
+    assert f(p, 0, 512, 2, 0, 7, None, 1, p, p, p, None) == 6            # rng mode
+    assert f(p, 0, 512, 2, 0, 3, None, 1, p, p, p, None) == 6            # external noise missing
+    assert f(p, 0, 0, 2, 0, 0, None, 1, p, p, p, None) == 0              # empty tensor: nothing to do
+    g = nv.lib.gact_dequantize
+    assert g(p, p, p, 0, 512, 5, p, None) == 1 and g(p, p, p, 4, 512, 2, p, None) == 2 and g(None, p, p, 0, 512, 2, p, None) == 3
+    assert nv.lib.gact_calc_precision(None, None, None, 0, 1.0, None, None) == 0
+    assert nv.lib.gact_calc_precision(None, None, None, 5, 1.0, None, None) == 3
+    assert nv.lib.gact_sq_diffs3_noalloc(p, p, None, 8, p, p, p, 5000, p, None) == 9      # more segments than it holds
+
+
+def test_import_fails_loudly_without_the_library(tmp_path, monkeypatch):
+    import importlib.util
+    import shutil
+    src = ROOT / "gact-icml_b200" / "gact" / "_native.py"
+    dst = tmp_path / "_native_copy.py"
+    shutil.copy(src, dst)
+    spec = importlib.util.spec_from_file_location("_native_copy", dst)
+    mod = importlib.util.module_from_spec(spec)
+    try:
+        spec.loader.exec_module(mod)
+    except ImportError as e:
+        assert "no fallback" in str(e)
+    else:
+        raise AssertionError("importing the binding next to no library must raise")
