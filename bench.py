@@ -2,6 +2,7 @@
 """Benchmark of the activation-compression hot path (quantize + dequantize GB/s).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--rng curand|fast|rtn]
+    python bench.py --workload bert_large|resnet50|gcn [--level L2] [--batch B]      (training samples/s)
 
 Workload (the kernel sweep the metric is quoted on): post-ReLU activations of shape
 128x64x112x112 in fp16 and bf16 at 1/2/4/8 bits, plus a mixed list of 50 fp16 tensors of 2^20..2^26 elements with
@@ -226,26 +227,34 @@ def run_ours(args):
             es = 2
             by = alg_bytes(n, bits, es, 4 if dt == torch.bfloat16 else 2)
             pk, mn, sc = bufs[i]
-            tq, td = [], []
-            for rep in range(7):
-                flush.zero_()
-                a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-                a.record(stream)
-                nv.lib.gact_quantize(xs[i].data_ptr(), nv.DTYPE_CODE[dt], n, bits, rep, mode, None, 1, pk.data_ptr(),
-                                     mn.data_ptr(), sc.data_ptr(), sp)
-                b.record(stream)
-                flush.zero_()
-                c0 = torch.cuda.Event(enable_timing=True); c0.record(stream)
-                nv.lib.gact_dequantize(pk.data_ptr(), mn.data_ptr(), sc.data_ptr(), nv.DTYPE_CODE[dt], n, bits,
-                                       out_big[(dt, n)].data_ptr(), sp)
-                c.record(stream)
-                torch.cuda.synchronize()
-                tq.append(a.elapsed_time(b)); td.append(c0.elapsed_time(c))
-            tq.sort(); td.sort()
-            table[name] = {"quantize_GBps": round(by / tq[3] / 1e6, 1), "dequantize_GBps": round(by / td[3] / 1e6, 1),
-                           "quantize_us": round(tq[3] * 1e3, 1), "dequantize_us": round(td[3] * 1e3, 1)}
-            print(f"[bench] {name:22s} quantize {tq[3]*1e3:8.1f} us {by/tq[3]/1e6:7.0f} GB/s | dequantize {td[3]*1e3:8.1f} us "
-                  f"{by/td[3]/1e6:7.0f} GB/s", file=sys.stderr)
+
+            def timed(fn):
+                ts = []
+                for rep in range(7):
+                    flush.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    fn(rep)
+                    e1.record(stream)
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1))
+                ts.sort()
+                return ts[3]
+
+            row = {}
+            for mname in ("fast", "curand", "rtn"):
+                m = nv.RNG_CODE[mname]
+                t = timed(lambda rep: nv.lib.gact_quantize(xs[i].data_ptr(), nv.DTYPE_CODE[dt], n, bits, rep, m, None, 1,
+                                                           pk.data_ptr(), mn.data_ptr(), sc.data_ptr(), sp))
+                row[f"quantize_{mname}_GBps"] = round(by / t / 1e6, 1)
+                row[f"quantize_{mname}_us"] = round(t * 1e3, 1)
+            t = timed(lambda rep: nv.lib.gact_dequantize(pk.data_ptr(), mn.data_ptr(), sc.data_ptr(), nv.DTYPE_CODE[dt], n, bits,
+                                                         out_big[(dt, n)].data_ptr(), sp))
+            row["dequantize_GBps"] = round(by / t / 1e6, 1)
+            row["dequantize_us"] = round(t * 1e3, 1)
+            table[name] = row
+            print(f"[bench] {name:20s} quantize fast {row['quantize_fast_GBps']:7.0f} curand {row['quantize_curand_GBps']:7.0f} "
+                  f"rtn {row['quantize_rtn_GBps']:7.0f} | dequantize {row['dequantize_GBps']:7.0f} GB/s", file=sys.stderr)
         del flush
 
     # ---- end-to-end arm: pinned host -> op_quantize -> op_dequantize -> host ---------------------------------
@@ -396,18 +405,111 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------------------------------------------
+def run_training(args):
+    """End-to-end training throughput (samples/s) of a synthetic-data workload with saved-tensor compression."""
+    import statistics
+
+    import gact
+    import gact.ops
+    import workloads
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    gact.config.reset()
+    gact.set_optimization_level(args.level)
+    gact.config.rng_mode = args.rng
+    gact.config.dp_probe = args.dp_probe
+    kw = {"world": world, "seed": rank}
+    if args.batch:
+        kw["batch"] = args.batch
+    if args.workload == "bert_large" and args.layers:
+        kw["layers"] = args.layers
+    wl = workloads.BUILDERS[args.workload](dev, **kw)
+    ctl = gact.Controller(wl.model)
+    ctl.install_hook()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    t_adapt0 = time.perf_counter()
+    loss = wl.step()
+    ctl.iterate(wl.backprop)                       # first iteration: the sensitivity probe + bit allocation
+    barrier()
+    adapt_s = time.perf_counter() - t_adapt0
+    for _ in range(max(args.warmup - 1, 0)):
+        loss = wl.step()
+        ctl.iterate(wl.backprop)
+    barrier()
+    torch.cuda.reset_peak_memory_stats()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = gact.ops.launch_count
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for k in range(args.steps):
+        loss = wl.step()
+        ctl.iterate(wl.backprop)
+        ev[k + 1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step = [ev[k].elapsed_time(ev[k + 1]) for k in range(args.steps)]
+    clocks = sampler.stop() if rank == 0 else None
+    launches = gact.ops.launch_count - launches0
+    peak_mem = torch.cuda.max_memory_allocated()
+    ctl.uninstall_hook()
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    total_ms = float(t.item())
+    if rank == 0:
+        value = world * wl.samples_per_step * args.steps / (total_ms * 1e-3)
+        bits = dict(ctl.quantizer.bits) if gact.config.compress_activation else {}
+        hist = {}
+        for b in bits.values():
+            hist[str(b)] = hist.get(str(b), 0) + 1
+        line = {"metric": f"GACT {wl.name} samples/s", "value": round(value, 2), "unit": "samples/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 3),
+                "median_ms_per_step": round(statistics.median(per_step), 3), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": wl.describe.get("autocast", "fp32"), "data": "synthetic",
+                "config": dict(wl.describe, workload=wl.name, level=args.level, rng=args.rng, dp_probe=args.dp_probe,
+                               parallelism=f"dp{world}"),
+                "compressed_tensors": len(bits), "bit_histogram": hist, "adapt_seconds": round(adapt_s, 2),
+                "peak_mem_GB": round(peak_mem / 2**30, 2), "final_loss": float(loss),
+                "gpu_launches": launches, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--rng", default="curand", choices=["curand", "fast", "rtn"])
+    ap.add_argument("--rng", default="fast", choices=["curand", "fast", "rtn"])
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "bert_large", "resnet50", "gcn"])
+    ap.add_argument("--level", default="L2", help="optimisation level of the training workloads (L0 = uncompressed)")
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch of the training workloads (0 = the workload's own)")
+    ap.add_argument("--layers", type=int, default=0, help="bert_large only: fewer encoder layers for quick runs")
+    ap.add_argument("--dp-probe", default="allreduce", choices=["allreduce", "local"])
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload != "sweep":
+        if not torch.cuda.is_available():
+            raise SystemExit("training workloads need a CUDA device")
+        return run_training(args)
     if args.impl == "reference":
         return run_reference(args)
     if not torch.cuda.is_available():

@@ -112,13 +112,19 @@ __global__ void __launch_bounds__(kDThreads) dequantize_kernel(const DequantArgs
                 if (full) st_stream_u4((uint16_t*)a.out + g * kGroup + lane * 8, make_uint4(w[0], w[1], w[2], w[3]));
                 else store_group8_slow<DT>(a.out, a.n, g, lane, o);
             } else {
-                // correctly rounded fp32 quotient from the reciprocal (Markstein); IEEE division for unusual scales
+                // fp32: correctly rounded quotient from the reciprocal (Markstein); IEEE division for unusual scales.
+                // bf16 (not a reference type): fma(code, 1/scale, min) in fp32, rounded once to bf16.
                 const uint32_t sb = __float_as_uint(s);
                 const bool fast = (sb - 0x21800000u) < (0x5D800000u - 0x21800000u);   // 2^-60 <= s < 2^60, s > 0
                 float o[8];
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const uint32_t word = (j < 4) ? c_lo : c_hi;
+                    if (DT == GACT_BF16) {
+                        const float c = byte_as_magic(word, j & 3) - kTwo23;
+                        o[j] = __fmaf_rn(c, r, m);
+                        continue;
+                    }
                     const float c = byte_as_magic(word, j & 3) - kTwo23;              // exact
                     float q;
                     if (fast) {

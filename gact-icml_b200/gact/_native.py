@@ -70,7 +70,13 @@ def require_cuda(t: torch.Tensor, name: str) -> None:
         raise RuntimeError(f"{name} must be a CUDA tensor!")       # same wording as the reference's check
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> int:
+    """cudaStream_t of torch's current stream on the current device."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

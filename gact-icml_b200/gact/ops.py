@@ -13,6 +13,10 @@ from gact.conf import config
 from gact import _native as nv
 
 
+# number of library kernels enqueued by this module (benchmarks report it)
+launch_count = 0
+
+
 def _numel(shape):
     n = 1
     for s in shape:
@@ -46,6 +50,8 @@ def quantize_pack(input, q_bit, seed, rng_mode=None, noise=None, fma=None):
         st = nv.lib.gact_quantize(x.data_ptr(), nv.DTYPE_CODE[x.dtype], n, q_bit, int(seed) & 0xFFFFFFFFFFFFFFFF, mode,
                                   noise_ptr, int(config.fma if fma is None else fma), q_input.data_ptr(),
                                   q_min.data_ptr(), q_scale.data_ptr(), nv.stream_ptr())
+    global launch_count
+    launch_count += 1
     nv.check(st, "gact_quantize")
     return q_input, q_scale, q_min
 
@@ -82,6 +88,8 @@ def dequantize_and_unpack(data, shape, q_bit, scale, mn):
     with nv.device_guard(data):
         st = nv.lib.gact_dequantize(data.data_ptr(), mn.data_ptr(), scale.data_ptr(), nv.DTYPE_CODE[mn.dtype], n, q_bit,
                                     out.data_ptr(), nv.stream_ptr())
+    global launch_count
+    launch_count += 1
     nv.check(st, "gact_dequantize")
     return out
 
@@ -99,6 +107,8 @@ def op_quantize_mask(input, flag=None):
     with nv.device_guard(x):
         st = nv.lib.gact_mask_pack(x.data_ptr(), n, words.data_ptr(), None if flag is None else flag.data_ptr(),
                                    nv.stream_ptr())
+    global launch_count
+    launch_count += 1
     nv.check(st, "gact_mask_pack")
     return [words, input.shape]
 
@@ -110,6 +120,8 @@ def op_dequantize_mask(input, dtype=torch.uint8):
     out = torch.empty(tuple(int(s) for s in input_shape), dtype=torch.uint8, device=q_mask.device)
     with nv.device_guard(q_mask):
         st = nv.lib.gact_mask_unpack(q_mask.data_ptr(), n, out.data_ptr(), nv.stream_ptr())
+    global launch_count
+    launch_count += 1
     nv.check(st, "gact_mask_unpack")
     return out if dtype == torch.uint8 else out.view(dtype)
 
@@ -142,3 +154,83 @@ def minimax(data):
         st = nv.lib.gact_minimax(x.data_ptr(), nv.DTYPE_CODE[x.dtype], x.numel(), mn.data_ptr(), mx.data_ptr(), nv.stream_ptr())
     nv.check(st, "gact_minimax")
     return mn, mx
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Compact payload used by the saved-tensor hooks: ONE allocation holds packed codes, per-group min and scale, and
+# the library is called with offsets into it.  A training step runs hundreds of hooks, each of them a few
+# microseconds of kernel time, so host overhead per call matters as much as the kernels.
+# ---------------------------------------------------------------------------------------------------------------
+_ELEM_SIZE = {torch.float32: 4, torch.float16: 2, torch.bfloat16: 2}
+_layout_cache = {}
+
+
+def _layout(n, bits, dtype):
+    key = (n, bits, dtype)
+    lay = _layout_cache.get(key)
+    if lay is None:
+        G = (n + nv.GROUP - 1) // nv.GROUP
+        nbytes = nv.lib.gact_packed_bytes(n, bits)
+        if nbytes < 0:
+            raise ValueError("bits must be 1, 2, 4, 8 or 32, got %r" % (bits,))
+        es = _ELEM_SIZE[dtype]
+        ss = 4 if dtype == torch.bfloat16 else es
+        off_min = (nbytes + 15) // 16 * 16
+        off_scale = (off_min + G * es + 15) // 16 * 16
+        lay = _layout_cache[key] = (G, nbytes, off_min, off_scale, off_scale + G * ss, nv.DTYPE_CODE[dtype])
+    return lay
+
+
+class Packed:
+    """Compressed tensor in one buffer.  Indexing gives the reference's list view
+    ``[q_input, q_bit, q_scale, q_min]`` (gact/gact/ops.py:57-59) for code that wants to look inside."""
+    __slots__ = ("buf", "bits", "dtype", "n")
+
+    def __init__(self, buf, bits, dtype, n):
+        self.buf, self.bits, self.dtype, self.n = buf, bits, dtype, n
+
+    def __getitem__(self, i):
+        G, nbytes, off_min, off_scale, total, _ = _layout(self.n, self.bits, self.dtype)
+        if i == 0:
+            return self.buf[:nbytes + 1].view(torch.int8)       # R*256 + 1 bytes, the last one unspecified, as in the reference
+        if i == 1:
+            return self.bits
+        sdt = torch.float32 if self.dtype == torch.bfloat16 else self.dtype
+        if i == 2:
+            return self.buf[off_scale:total].view(sdt).reshape(G, 1, 1)
+        if i == 3:
+            return self.buf[off_min:off_min + G * _ELEM_SIZE[self.dtype]].view(self.dtype).reshape(G, 1, 1)
+        raise IndexError(i)
+
+    def __len__(self):
+        return 4
+
+
+def quantize_compact(input, q_bit, seed):
+    """Fused quantize into a single-buffer payload (the hooks' fast path)."""
+    x = input if input.is_contiguous() else input.contiguous()
+    n = x.numel()
+    G, nbytes, off_min, off_scale, total, code = _layout(n, q_bit, x.dtype)
+    buf = torch.empty(total, dtype=torch.uint8, device=x.device)
+    base = buf.data_ptr()
+    with nv.device_guard(x):
+        st = nv.lib.gact_quantize(x.data_ptr(), code, n, q_bit, int(seed) & 0xFFFFFFFFFFFFFFFF, nv.RNG_CODE[config.rng_mode],
+                                  None, int(config.fma), base, base + off_min, base + off_scale, nv.stream_ptr())
+    global launch_count
+    launch_count += 1
+    if st:
+        nv.check(st, "gact_quantize")
+    return Packed(buf, q_bit, x.dtype, n)
+
+
+def dequantize_compact(p, shape):
+    G, nbytes, off_min, off_scale, total, code = _layout(p.n, p.bits, p.dtype)
+    out = torch.empty(shape, dtype=p.dtype, device=p.buf.device)
+    base = p.buf.data_ptr()
+    with nv.device_guard(out):
+        st = nv.lib.gact_dequantize(base, base + off_min, base + off_scale, code, p.n, p.bits, out.data_ptr(), nv.stream_ptr())
+    global launch_count
+    launch_count += 1
+    if st:
+        nv.check(st, "gact_dequantize")
+    return out

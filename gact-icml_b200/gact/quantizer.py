@@ -9,6 +9,7 @@ import torch
 
 from gact.conf import config
 from gact.ops import op_quantize, op_dequantize, op_quantize_mask, op_dequantize_mask
+from gact import ops as _ops
 from gact.utils import uniform_sample
 
 
@@ -58,6 +59,8 @@ class Quantizer:
     # returns (should_be_quantized, is_dropout_mask)
     def check_quantize(self, input_tensor):
         # parameters are not compressed
+        if input_tensor.layout != torch.strided:            # sparse tensors are left alone
+            return False, False
         if input_tensor.data_ptr() in self.unrelated_tensors:
             return False, False
         # 0/1 byte tensors (dropout masks) take the 1-bit path
@@ -138,7 +141,11 @@ class Quantizer:
                 self.seeds[tid] = tid
             else:
                 bit = self.bits[tid]
-            q_inputs = op_quantize(input, bit, self.seeds[tid] + self.seed_iter + self.seed_offset)
+            seed = self.seeds[tid] + self.seed_iter + self.seed_offset
+            if bit == 32:
+                q_inputs = op_quantize(input, bit, seed)
+            else:
+                q_inputs = _ops.quantize_compact(input, bit, seed)
             if self.swap:
                 self._swap_out(q_inputs)
             self.ptr_qtensor_map[key] = [q_inputs, 1, tid]
@@ -146,16 +153,27 @@ class Quantizer:
             entry[1] += 1       # same tensor saved again: share the payload
         return True, is_dropout_mask, key, input_shape, tid
 
+    @staticmethod
+    def _payload(q):
+        return q.buf if type(q) is _ops.Packed else q[0]
+
+    @staticmethod
+    def _set_payload(q, t):
+        if type(q) is _ops.Packed:
+            q.buf = t
+        else:
+            q[0] = t
+
     def _swap_out(self, q_inputs):
         # device -> pinned host copy of the packed bytes on the side stream, ordered after the kernel that
         # produced them; the device buffer is handed back to the allocator once the copy has been queued.
-        q_gpu = q_inputs[0]
+        q_gpu = self._payload(q_inputs)
         self.swap_out_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.swap_out_stream):
             q_cpu = torch.empty(q_gpu.shape, dtype=q_gpu.dtype, device="cpu", pin_memory=True)
             q_cpu.copy_(q_gpu, non_blocking=True)
         q_gpu.record_stream(self.swap_out_stream)
-        q_inputs[0] = q_cpu
+        self._set_payload(q_inputs, q_cpu)
 
     def dequantize(self, input):
         quantized = input[0]
@@ -178,18 +196,21 @@ class Quantizer:
                 self.start_bwd = False
             if self.prefetch:
                 cur.wait_stream(self.swap_in_stream)       # a prefetch of this tensor may be in flight
-            if not q_inputs[0].is_cuda:
-                q_inputs[0] = q_inputs[0].cuda(non_blocking=True)
+            if not self._payload(q_inputs).is_cuda:
+                self._set_payload(q_inputs, self._payload(q_inputs).cuda(non_blocking=True))
             if self.prefetch and tid > 0:
                 previous_key = self.layer_key_map.get(tid - 1)
                 prev = self.ptr_qtensor_map.get(previous_key) if previous_key is not None else None
-                if prev is not None and not prev[0][0].is_cuda:
+                if prev is not None and not self._payload(prev[0]).is_cuda:
                     self.swap_in_stream.wait_stream(cur)
                     with torch.cuda.stream(self.swap_in_stream):
-                        prev[0][0] = prev[0][0].cuda(non_blocking=True)
-                    prev[0][0].record_stream(cur)
+                        self._set_payload(prev[0], self._payload(prev[0]).cuda(non_blocking=True))
+                    self._payload(prev[0]).record_stream(cur)
 
-        ret = op_dequantize(q_inputs, input_shape)
+        if type(q_inputs) is _ops.Packed:
+            ret = _ops.dequantize_compact(q_inputs, input_shape)
+        else:
+            ret = op_dequantize(q_inputs, input_shape)
 
         ref_cnt -= 1
         if ref_cnt < 0:

@@ -84,8 +84,8 @@ int gact_quantize(const void* x, int dtype, int64_t n, int bits, uint64_t seed, 
 int gact_pipeline_error(void);
 
 /*
- * Unpack + dequantize: out[i] = T(T(code)/scale) + min for the first n elements (bf16: fp32 divide and add,
- * one rounding to bf16; qscale is fp32 as written by gact_quantize).
+ * Unpack + dequantize: out[i] = T(T(code)/scale) + min for the first n elements (bf16, not a reference type:
+ * bf16(fma(code, fl32(1/scale), min)) with the fp32 qscale written by gact_quantize).
  * Replaces unpack_single_precision() (gact/gact/cpp_extension/quantization.cc:36-49,
  * quantization_cuda_kernel.cu:149-221) and the slice in gact/gact/ops.py:61-69.
  *   out     n elements of `dtype`, 16-byte aligned (no padded tail is written)

@@ -307,7 +307,8 @@ int oracle_quantize(const void *x, int dtype, int64_t n, int bits, uint64_t seed
 
 /* ------------------------------------------------------------------------------------------------
  * dequantize (quantization_cuda_kernel.cu:166-175): out = T(T(code) / scale) + min, each op rounded to T
- * (fp32: IEEE divide, add; bf16: fp32 divide and add, then one rounding).  Writes the first n elements.
+ * (fp32: IEEE divide, add; bf16, which is not a reference type: fma(code, fl32(1/scale), min) in fp32, then one
+ * rounding to bf16).  Writes the first n elements.
  * ---------------------------------------------------------------------------------------------- */
 int oracle_dequantize(const uint8_t *packed, const void *qmin, const void *qscale, int dtype, int64_t n,
                       int bits, void *out) {
@@ -323,8 +324,8 @@ int oracle_dequantize(const uint8_t *packed, const void *qmin, const void *qscal
         const int ni = (int)(g % wpt);
         const int code = (packed[r * GROUP + d] >> (ni * bits)) & mask;
         const float s = load_elem(qscale, scale_dtype(dtype), g), m = load_elem(qmin, dtype, g);
-        if (dtype == DT_BF16) {                                  /* fp32 arithmetic, one rounding to bf16 at the end */
-            store_elem(out, dtype, i, ((float)code / s) + m);
+        if (dtype == DT_BF16) {                                  /* ours: fma(code, fl32(1/scale), min), one rounding to bf16 */
+            store_elem(out, dtype, i, fmaf((float)code, 1.0f / s, m));
             continue;
         }
         const float c = round_T((float)code, dtype);             /* exact for codes <= 255 in every T */

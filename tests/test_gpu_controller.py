@@ -11,6 +11,11 @@ from helpers import assert_bits_equal
 pytestmark = pytest.mark.gpu
 
 
+def gact_mode():
+    import gact
+    return gact.config.rng_mode
+
+
 def error_rate(q, x):
     return (((q - x) ** 2).sum() / (x ** 2).sum()).item()
 
@@ -67,7 +72,7 @@ def test_op_contract_matches_oracle_front_end():
     for dtype in (torch.float32, torch.float16, torch.bfloat16):
         x_cpu = torch.randn(7, 33, 129).to(dtype)
         q = op_quantize(x_cpu.cuda(), 2, 5)
-        oq = oracle.op_quantize(x_cpu, 2, 5)
+        oq = oracle.op_quantize(x_cpu, 2, 5, rng_mode=gact_mode())
         assert q[0].shape == oq[0].shape and q[0].dtype == torch.int8
         assert q[2].shape == oq[2].shape and q[3].shape == oq[3].shape and q[3].dtype == dtype
         assert q[2].dtype == (torch.float32 if dtype == torch.bfloat16 else dtype)
@@ -115,7 +120,7 @@ def test_full_size_properties_config2():
         assert not torch.equal(q[:-1], q3[:-1])
         # oracle on the first 2048 groups (row-blocks are independent of what follows them)
         k = 2048 * 256
-        opk, omn, osc = oracle.quantize(x.reshape(-1)[:k].cpu(), bits, 42)
+        opk, omn, osc = oracle.quantize(x.reshape(-1)[:k].cpu(), bits, 42, gact_mode())
         nb = opk.numel()
         assert torch.equal(q[:nb].cpu().view(torch.uint8), opk)
         assert_bits_equal(sc.reshape(-1)[:2048], osc, "scale")

@@ -90,7 +90,7 @@ def test_quantizer_tuples_tids_seeds_and_refcounts(fake):
     assert q.tid == 2
     # payload matches the oracle with seed = seeds[tid] + seed_iter
     q_inputs, ref, tid = q.ptr_qtensor_map[1]
-    want = oracle.op_quantize(x1.detach(), 2, 1 + 0)
+    want = oracle.op_quantize(x1.detach(), 2, 1 + 0, rng_mode=config.rng_mode)
     assert ref == 1 and tid == 1 and torch.equal(q_inputs[0][:-1], want[0][:-1])
     y1 = q.dequantize(r1)
     assert y1.shape == x1.shape and y1.dtype == torch.float16
@@ -104,7 +104,7 @@ def test_quantizer_tuples_tids_seeds_and_refcounts(fake):
     q.bits[0] = 8
     r = q.quantize(x0)
     assert r[4] == 0 and q.ptr_qtensor_map[0][0][1] == 8
-    want = oracle.op_quantize(x0.detach(), 8, 0 + 5)
+    want = oracle.op_quantize(x0.detach(), 8, 0 + 5, rng_mode=config.rng_mode)
     assert torch.equal(q.ptr_qtensor_map[0][0][0][:-1], want[0][:-1])
     # a tensor that was never registered in iteration 0 is an error, as in the reference (static graph)
     q.quantize(x1)
