@@ -120,11 +120,19 @@ class Quantizer:
         return True, True, q_inputs
 
     def quantize(self, input):
-        quantize, is_dropout_mask = self.check_quantize(input)
-        if not quantize:
-            return False, input
-        if is_dropout_mask:
-            return self._quantize_mask(input)
+        # Same decisions as check_quantize, cheapest tests first: this runs for every saved tensor of every step.
+        dt = input.dtype
+        if dt is torch.float32 or dt is torch.float16 or (dt is torch.bfloat16 and config.quantize_bf16):
+            if (not input.requires_grad) or input.layout is not torch.strided or not (2 <= input.dim() <= 4) \
+                    or not self._on_device(input) or input.data_ptr() in self.unrelated_tensors:
+                return False, input
+            is_dropout_mask = False
+        else:
+            quantize, is_dropout_mask = self.check_quantize(input)
+            if not quantize:
+                return False, input
+            if is_dropout_mask:
+                return self._quantize_mask(input)
 
         tid = self.tid
         self.tid += 1
