@@ -183,11 +183,13 @@ def _layout(n, bits, dtype):
 
 class Packed:
     """Compressed tensor in one buffer.  Indexing gives the reference's list view
-    ``[q_input, q_bit, q_scale, q_min]`` (gact/gact/ops.py:57-59) for code that wants to look inside."""
-    __slots__ = ("buf", "bits", "dtype", "n")
+    ``[q_input, q_bit, q_scale, q_min]`` (gact/gact/ops.py:57-59) for code that wants to look inside.
+    ``strides`` is None for a contiguous source, else the strides of the dense, permuted source whose memory
+    order was compressed (the reconstruction is laid out the same way)."""
+    __slots__ = ("buf", "bits", "dtype", "n", "strides")
 
-    def __init__(self, buf, bits, dtype, n):
-        self.buf, self.bits, self.dtype, self.n = buf, bits, dtype, n
+    def __init__(self, buf, bits, dtype, n, strides=None):
+        self.buf, self.bits, self.dtype, self.n, self.strides = buf, bits, dtype, n, strides
 
     def __getitem__(self, i):
         G, nbytes, off_min, off_scale, total, _ = _layout(self.n, self.bits, self.dtype)
@@ -206,9 +208,39 @@ class Packed:
         return 4
 
 
+_dense_cache = {}
+
+
+def _is_dense_permutation(shape, strides):
+    """True when the strides describe a permutation of a contiguous block (no gaps, no overlap)."""
+    key = (shape, strides)
+    r = _dense_cache.get(key)
+    if r is None:
+        dims = sorted((st, sz) for st, sz in zip(strides, shape) if sz != 1)
+        expect, r = 1, True
+        for st, sz in dims:
+            if st != expect:
+                r = False
+                break
+            expect *= sz
+        _dense_cache[key] = r
+    return r
+
+
 def quantize_compact(input, q_bit, seed):
-    """Fused quantize into a single-buffer payload (the hooks' fast path)."""
-    x = input if input.is_contiguous() else input.contiguous()
+    """Fused quantize into a single-buffer payload (the hooks' fast path).
+
+    A non-contiguous but dense tensor (a transposed / permuted view, as attention layers save them) is compressed
+    in MEMORY order, without the contiguous copy that the reference's ``reshape(-1, 256)`` makes: the groups are
+    256 neighbouring elements of memory instead of 256 neighbouring elements of the logical order, and the
+    reconstruction comes back with the source's strides.  ``config.keep_layout = False`` restores the copy."""
+    strides = None
+    if input.is_contiguous():
+        x = input
+    elif config.keep_layout and (input.data_ptr() & 15) == 0 and _is_dense_permutation(tuple(input.shape), input.stride()):
+        x, strides = input, input.stride()
+    else:
+        x = input.contiguous()
     n = x.numel()
     G, nbytes, off_min, off_scale, total, code = _layout(n, q_bit, x.dtype)
     buf = torch.empty(total, dtype=torch.uint8, device=x.device)
@@ -220,12 +252,15 @@ def quantize_compact(input, q_bit, seed):
     launch_count += 1
     if st:
         nv.check(st, "gact_quantize")
-    return Packed(buf, q_bit, x.dtype, n)
+    return Packed(buf, q_bit, x.dtype, n, strides)
 
 
 def dequantize_compact(p, shape):
     G, nbytes, off_min, off_scale, total, code = _layout(p.n, p.bits, p.dtype)
-    out = torch.empty(shape, dtype=p.dtype, device=p.buf.device)
+    if p.strides is None:
+        out = torch.empty(shape, dtype=p.dtype, device=p.buf.device)
+    else:
+        out = torch.empty_strided(shape, p.strides, dtype=p.dtype, device=p.buf.device)
     base = p.buf.data_ptr()
     with nv.device_guard(out):
         st = nv.lib.gact_dequantize(base, base + off_min, base + off_scale, code, p.n, p.bits, out.data_ptr(), nv.stream_ptr())

@@ -5,6 +5,8 @@ width and seed, and keeps the compressed payloads in a ref-counted map until bac
 The tuples handed to autograd keep the reference's formats:
 ``(False, tensor)`` | ``(True, True, [mask_words, shape])`` | ``(True, False, key, shape, tid)``.
 """
+import weakref
+
 import torch
 
 from gact.conf import config
@@ -46,6 +48,8 @@ class Quantizer:
         # added to every seed so that data-parallel ranks draw independent noise (0 on a single process)
         self.seed_offset = 0
         self._mask_flag = None
+        # tensors compressed in this forward pass, by object identity: id -> (weak reference, version, key)
+        self._live = {}
 
     def filter_tensors(self, pairs):
         for _, v in pairs:
@@ -92,6 +96,7 @@ class Quantizer:
     def iterate(self):
         self.ptr_qtensor_map = {}
         self.layer_key_map = {}
+        self._live = {}
         self.tid = 0
         self.start_bwd = True
         self.iter += 1
@@ -138,7 +143,16 @@ class Quantizer:
         self.tid += 1
         input_shape = input.shape
 
-        key = self.generate_tensor_key(input, tid)
+        # The same tensor object saved again, unmodified (e.g. one activation feeding three linear layers): share
+        # the payload of its first save.  Identity + version counter decide it, so nothing is read back from the
+        # device (the reference's check_dup fingerprints the values and synchronises for it).
+        seen = self._live.get(id(input)) if config.dedup_saved else None
+        if seen is not None and seen[0]() is input and seen[1] == input._version and seen[2] in self.ptr_qtensor_map:
+            key = seen[2]
+        else:
+            key = self.generate_tensor_key(input, tid)
+            if config.dedup_saved:
+                self._live[id(input)] = (weakref.ref(input), input._version, key)
         self.layer_key_map[tid] = key
         entry = self.ptr_qtensor_map.get(key)
         if entry is None:

@@ -205,7 +205,7 @@ def test_auto_precision_end_to_end_on_cpu(fake):
     assert [ctl.quantizer.bits[l] for l in l_list] == want.tolist()
     assert all(np.isfinite(losses))
     # probing must leave the table of seeds untouched and the bits consistent with the allocation
-    assert ctl.quantizer.seeds == {l: l for l in l_list}
+    assert ctl.quantizer.seeds == {l: l for l in l_list}      # seeds[tid] = tid; duplicates register nothing
 
 
 def test_probe_matches_reference_formula(fake):
@@ -240,7 +240,7 @@ def test_probe_matches_reference_formula(fake):
 
         saved_bits = dict(q.bits)
         q.bits = {l: q.default_bit for l in saved_bits}        # the probe ran with the default widths elsewhere
-        l = 1
+        l = list(saved_bits)[1]
         g0, g1, g2 = grad_with(l, 1, 0), grad_with(l, 1, 1), grad_with(l, 8, 0)
         want = max(float(((g0 - g1) ** 2).sum()), 2 * max(float(((g0 - g2) ** 2).sum()), float(((g1 - g2) ** 2).sum())))
         assert ctl.ap.C[l] == pytest.approx(want, rel=1e-4)
@@ -265,3 +265,48 @@ def test_utils():
     assert compute_tensor_bytes([torch.zeros(3, 4), torch.zeros(5, dtype=torch.int8), 7, torch.zeros(2, dtype=torch.bfloat16)]) == 48 + 5 + 4 + 4
     exp_recorder.record("x", np.float32(1.23456789))
     assert exp_recorder.val_dict["x"] == 1.234568
+
+
+def test_same_tensor_saved_twice_shares_one_payload_without_reading_it(fake):
+    q = Quantizer(4, False, False)
+    x = torch.randn(16, 256, requires_grad=True)
+    a, b = q.quantize(x), q.quantize(x)
+    assert a[2] == b[2] and (a[4], b[4]) == (0, 1) and len(q.ptr_qtensor_map) == 1
+    assert q.ptr_qtensor_map[a[2]][1] == 2 and list(q.bits) == [0]           # the duplicate registers no width of its own
+    y = x.detach().clone().requires_grad_()
+    c = q.quantize(y)                                                        # equal values, other object: not shared
+    assert c[2] != a[2]
+    with torch.no_grad():
+        x.add_(1.0)                                                          # modified in place: version moved on
+    d = q.quantize(x)
+    assert d[2] != a[2]
+    for r in (a, b, c, d):
+        q.dequantize(r)
+    assert not q.ptr_qtensor_map
+    config.dedup_saved = False
+    q = Quantizer(4, False, False)
+    a, b = q.quantize(x), q.quantize(x)
+    assert a[2] != b[2]
+
+
+def test_dense_permuted_views_are_compressed_in_memory_order(fake):
+    q = Quantizer(8, False, False)
+    base = torch.randn(4, 6, 32, 16)
+    x = base.transpose(1, 2).requires_grad_()                 # dense, not contiguous
+    assert not x.is_contiguous()
+    r = q.quantize(x)
+    payload = q.ptr_qtensor_map[r[2]][0]
+    assert payload.strides == x.stride()
+    want = oracle.quantize(base.reshape(-1), 8, 0, config.rng_mode)[0]          # memory order = the base tensor's order
+    assert torch.equal(payload[0][:-1].view(torch.uint8), want)
+    y = q.dequantize(r)
+    assert y.shape == x.shape and y.stride() == x.stride()
+    assert float((y - x).abs().max()) < 0.05
+    # a view with gaps is not dense: it takes the copy
+    z = torch.randn(8, 64, 40)[:, :, :32].requires_grad_()
+    r = q.quantize(z)
+    assert q.ptr_qtensor_map[r[2]][0].strides is None
+    assert float((q.dequantize(r) - z).abs().max()) < 0.05
+    config.keep_layout = False
+    r = q.quantize(x)
+    assert q.ptr_qtensor_map[r[2]][0].strides is None
