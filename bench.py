@@ -83,7 +83,7 @@ def spec_bytes(spec):
 
 # ----------------------------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -96,7 +96,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -348,7 +348,7 @@ def run_ours(args):
             "kernels": table,
         }
         if not args.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline(spec, sample_elems=1 << 22, reps=1)
+            line["cpu_baseline"] = cpu_baseline(spec, sample_elems=1 << 24, reps=6)
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.barrier()
@@ -439,6 +439,7 @@ def run_training(args):
     gact.set_optimization_level(args.level)
     gact.config.rng_mode = args.rng
     gact.config.dp_probe = args.dp_probe
+    workloads.DDP_BUCKET_MB = args.bucket_mb
     kw = {"world": world, "seed": rank}
     if args.batch:
         kw["batch"] = args.batch
@@ -495,7 +496,7 @@ def run_training(args):
                 "median_ms_per_step": round(statistics.median(per_step), 3), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": wl.describe.get("autocast", "fp32"), "data": "synthetic",
                 "config": dict(wl.describe, workload=wl.name, level=args.level, rng=args.rng, dp_probe=args.dp_probe,
-                               parallelism=f"dp{world}"),
+                               parallelism=f"dp{world}", ddp_bucket_mb=args.bucket_mb),
                 "compressed_tensors": len(bits), "bit_histogram": hist, "adapt_seconds": round(adapt_s, 2),
                 "peak_mem_GB": round(peak_mem / 2**30, 2), "final_loss": float(loss),
                 "gpu_launches": launches, "clocks": clocks}
@@ -508,7 +509,7 @@ def run_training(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 200 for the sweep, 20 for training)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rng", default="fast", choices=["curand", "fast", "rtn"])
@@ -517,11 +518,14 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch of the training workloads (0 = the workload's own)")
     ap.add_argument("--layers", type=int, default=0, help="bert_large only: fewer encoder layers for quick runs")
     ap.add_argument("--dp-probe", default="allreduce", choices=["allreduce", "local"])
+    ap.add_argument("--bucket-mb", type=int, default=100, help="DDP gradient bucket size of the training workloads")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.steps is None:
+        args.steps = 20 if args.workload != "sweep" else (200 if args.impl == "ours" else 5)
     if args.workload != "sweep":
         if not torch.cuda.is_available():
             raise SystemExit("training workloads need a CUDA device")

@@ -401,8 +401,10 @@ static int launch_quantize(const QuantArgs& args, cudaStream_t s) {
                 per_sm = 1;
             pipe_resident = per_sm * kSMs;
         }
+        // one resident wave, with the chunks spread evenly: every CTA gets the same number of chunks (+-1)
         const int64_t cap = pipe_resident;
-        const int blocks = (int)(nchunks < cap ? nchunks : cap);
+        const int64_t rounds = (nchunks + cap - 1) / cap;
+        const int blocks = (int)((nchunks + rounds - 1) / rounds);
         quantize_pipe_kernel<DT, BITS, RNG, FMA><<<blocks, kPipeThreads, kPipeStages * kChunkBytes, s>>>(a, nchunks);
         if (cudaGetLastError() != cudaSuccess) return GACT_ERR_LAUNCH;
         a.tile_begin = nchunks * kPipeWarps;

@@ -30,9 +30,13 @@ class Workload:
     describe: dict
 
 
+DDP_BUCKET_MB = 25          # torch's default; benchmarks may raise it (fewer, larger NVLink all-reduces)
+
+
 def _wrap_ddp(model, device, world):
     if world > 1:
-        return nn.parallel.DistributedDataParallel(model, device_ids=[device.index], gradient_as_bucket_view=True)
+        return nn.parallel.DistributedDataParallel(model, device_ids=[device.index], gradient_as_bucket_view=True,
+                                                   bucket_cap_mb=DDP_BUCKET_MB)
     return model
 
 
