@@ -42,17 +42,39 @@ template <int DT, int BITS> struct Tile {
     static constexpr int U = GPW / WPT;
 };
 
+// Which noise values reach codes8 "centred" (noise - 0.5 instead of noise).  With the 8-bit noise of FAST and the
+// constant noise of RTN, and p a half-precision value, p + noise is exact in fp32, so (p + noise) - 0.5 equals
+// p + (noise - 0.5) bit for bit and one addition is saved; bf16 (not a reference type) is defined on centred
+// noise in every mode.  fp32 keeps the reference's order of operations.
+template <int DT, int RNG> struct Centred {
+    static constexpr bool value = (DT == GACT_BF16) || (DT == GACT_F16 && (RNG == GACT_RNG_FAST || RNG == GACT_RNG_RTN));
+};
+// FAST and RTN never produce a code above 2^bits - 1 (fp16: clamped, see codes8; fp32 / bf16: the noise stays
+// below 1), so slots cannot collide and the packed byte may be summed instead of OR-ed.
+template <int RNG> struct NoOverflow { static constexpr bool value = (RNG == GACT_RNG_FAST || RNG == GACT_RNG_RTN); };
+
 // noise of the FAST arrangement: one Philox4x32-10 call, counter (block_lo, block_hi, 0, "FAST"), gives 16
 // bytes = 8 bits for each of this lane's 8 elements of an even group (bytes 0..7) and of the following odd group
-// (bytes 8..15); noise = (byte + 0.5) / 256.  The bytes go to float on the conversion unit.
+// (bytes 8..15); noise = (byte + 0.5) / 256 (minus 0.5 when CENTRED).  The bytes go to float on the conversion unit.
+template <bool CENTRED>
 __device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& rk, float2 (&even)[4], float2 (&odd)[4]) {
     const uint4 r = philox4x32_10((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-    const float2 s2 = splat2(0.00390625f), o2 = splat2(0.001953125f);
+#ifdef GACT_NOISE_I2F
+    const float2 s2 = splat2(0.00390625f), o2 = splat2(CENTRED ? -0.498046875f : 0.001953125f);
+#else
+    // 2^23 + byte by byte permute, then (2^23 + b) / 256 - 2^15 + offset in one exact multiply-add
+    const float2 s2 = splat2(0.00390625f), o2 = splat2((CENTRED ? -0.498046875f : 0.001953125f) - 32768.0f);
+#endif
 #pragma unroll
     for (int i = 0; i < 4; i++) {
+#ifdef GACT_NOISE_I2F
         const float b0 = __uint2float_rn(w[i] & 0xffu), b1 = __uint2float_rn((w[i] >> 8) & 0xffu);
         const float b2 = __uint2float_rn((w[i] >> 16) & 0xffu), b3 = __uint2float_rn(w[i] >> 24);
+#else
+        const float b0 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7540u)), b1 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7541u));
+        const float b2 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7542u)), b3 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7543u));
+#endif
         float2 (&dst)[4] = (i < 2) ? even : odd;
         dst[(2 * i) & 3] = fma2(make_float2(b0, b1), s2, o2);
         dst[(2 * i + 1) & 3] = fma2(make_float2(b2, b3), s2, o2);
@@ -60,29 +82,39 @@ __device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& r
 }
 
 // magic bits (code in the low mantissa bits of 1.5*2^23 + code) of the 8 codes of one group held by this
-// lane; nz[i] = noise of elements 2i, 2i+1
-template <int DT, int BITS, bool FMA>
+// lane; nz[i] = noise of elements 2i, 2i+1 (centred where Centred<DT, RNG> says so)
+template <int DT, int BITS, int RNG, bool FMA>
 __device__ __forceinline__ void codes8(const uint32_t (&raw)[RawRegs<DT>::N], float mn, float sc, const float2 (&nz)[4],
                                        uint32_t (&cb)[8]) {
+    constexpr bool CENTRED = Centred<DT, RNG>::value;
+    constexpr float MAXC = (float)((1 << BITS) - 1);
     if constexpr (DT == GACT_F16) {
         if (isinf(sc)) {
             // A half-precision scale overflows to +inf when the group's range is below (2^b-1)/65504.  The
             // reference then computes t*inf: +inf for every element above the minimum, which __float2int_rn
             // saturates to 0x7fffffff (all ones from the slot upwards), and NaN -> 0 for the minimum itself.
+            // FAST / RTN clamp codes at 2^b - 1 instead.
             float v[8];
             raw_to_float<DT>(raw, v);
 #pragma unroll
-            for (int j = 0; j < 8; j++) cb[j] = (Elem<DT>::round(__fsub_rn(v[j], mn)) > 0.0f) ? 0x7fffffffu : 0u;
+            for (int j = 0; j < 8; j++)
+                cb[j] = (Elem<DT>::round(__fsub_rn(v[j], mn)) > 0.0f) ? (NoOverflow<RNG>::value ? (uint32_t)MAXC : 0x7fffffffu) : 0u;
             return;
         }
         const __half2 mn2 = __float2half2_rn(mn), sc2 = __float2half2_rn(sc);     // exact: both are half values
-        const __half2 zero2 = __float2half2_rn(0.0f);
+        const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const __half2 t = __hsub2(*(const __half2*)&raw[i], mn2);
-            const __half2 p = __hmax2(__hmul2(t, sc2), zero2);                    // NaN -> 0, as max(., 0) does
-            // u = p + noise; w = u - 0.5 (> -0.5, so no clamp needed: it rounds to 0); w + magic
-            const float2 r = add2(add2(add2(__half22float2(p), nz[i]), splat2(-0.5f)), splat2(kMagic));
+            __half2 p = __hmax2(__hmul2(t, sc2), zero2);                          // NaN -> 0, as max(., 0) does
+            // The reference has no upper clamp: when the half-precision scale rounded up, the group maximum can
+            // reach code 2^b and wrap / spill.  The reference stream (CURAND) and EXTERNAL reproduce that; FAST
+            // and RTN clamp p at 2^b - 1, which caps the code as well.
+            if (NoOverflow<RNG>::value) p = __hmin2(p, maxc2);
+            float2 r;
+            if (RNG == GACT_RNG_RTN) r = add2(__half22float2(p), splat2(kMagic));                 // (p + 0.5) - 0.5 = p
+            else if (CENTRED) r = add2(add2(__half22float2(p), nz[i]), splat2(kMagic));           // p + (noise - 0.5)
+            else r = add2(add2(add2(__half22float2(p), nz[i]), splat2(-0.5f)), splat2(kMagic));   // u - 0.5 > -0.5 rounds to 0
             cb[2 * i] = __float_as_uint(r.x);
             cb[2 * i + 1] = __float_as_uint(r.y);
         }
@@ -93,12 +125,16 @@ __device__ __forceinline__ void codes8(const uint32_t (&raw)[RawRegs<DT>::N], fl
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const float2 t = add2(make_float2(v[2 * i], v[2 * i + 1]), nmn);          // x - mn
-            const float2 u = (FMA || DT == GACT_BF16) ? fma2(t, sc2, nz[i]) : add2(mul2(t, sc2), nz[i]);
-            float2 w = add2(u, splat2(-0.5f));
-            w.x = fmaxf(w.x, 0.0f); w.y = fmaxf(w.y, 0.0f);                           // NaN -> 0
+            float2 w;
             if (DT == GACT_BF16) {
-                // ours: clamp at 2^bits - 1 (fp32 / fp16 keep the reference's missing clamp)
-                w.x = fminf(w.x, (float)((1 << BITS) - 1)); w.y = fminf(w.y, (float)((1 << BITS) - 1));
+                // ours: u = fma(t, scale, noise - 0.5), clamped to [0, 2^bits - 1]
+                w = fma2(t, sc2, nz[i]);
+                w.x = fmaxf(w.x, 0.0f); w.y = fmaxf(w.y, 0.0f);                       // NaN -> 0
+                if (!NoOverflow<RNG>::value) { w.x = fminf(w.x, MAXC); w.y = fminf(w.y, MAXC); }
+            } else {
+                const float2 u = FMA ? fma2(t, sc2, nz[i]) : add2(mul2(t, sc2), nz[i]);
+                w = add2(u, splat2(-0.5f));
+                w.x = fmaxf(w.x, 0.0f); w.y = fmaxf(w.y, 0.0f);                       // NaN -> 0; no upper clamp (reference)
             }
             const float2 r = add2(w, splat2(kMagic));
             cb[2 * i] = __float_as_uint(r.x);
@@ -184,6 +220,13 @@ __device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, i
                         nz[3][i] = fma2(make_float2(__uint2float_rn(ra.w), __uint2float_rn(rb.w)), s2, o2);
                     }
                 }
+                if (Centred<DT, RNG>::value) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            if (q < WPT) nz[q][i] = add2(nz[q][i], splat2(-0.5f));
+                }
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
                     const int ni = c * 4 + q;
@@ -191,7 +234,7 @@ __device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, i
                     const int k = u * WPT + ni;
                     if (!FULL && g0 + k >= a.G) break;         // tail row-block: absent groups leave zero bits
                     uint32_t cb[8];
-                    codes8<DT, BITS, FMA>(raw[k], mn[k], sc[k], nz[q], cb);
+                    codes8<DT, BITS, RNG, FMA>(raw[k], mn[k], sc[k], nz[q], cb);
 #pragma unroll
                     for (int j = 0; j < 8; j++) acc[j] |= cb[j] << (ni * BITS);
                 }
@@ -205,23 +248,26 @@ __device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, i
                 float2 nz[4];
                 if (RNG == GACT_RNG_FAST) {
                     if ((k & 1) == 0) {
-                        fast_noise16((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
+                        fast_noise16<Centred<DT, RNG>::value>((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
                     } else {
 #pragma unroll
                         for (int i = 0; i < 4; i++) nz[i] = nz_odd[i];
                     }
                 } else if (RNG == GACT_RNG_RTN) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) nz[i] = splat2(0.5f);
+                    for (int i = 0; i < 4; i++) nz[i] = splat2(Centred<DT, RNG>::value ? 0.0f : 0.5f);
                 } else {
                     const float2* p = (const float2*)(a.noise + (g0 + k) * kGroup + lane * 8);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) nz[i] = p[i];
+                    for (int i = 0; i < 4; i++) nz[i] = Centred<DT, RNG>::value ? add2(p[i], splat2(-0.5f)) : p[i];
                 }
                 uint32_t cb[8];
-                codes8<DT, BITS, FMA>(raw[k], mn[k], sc[k], nz, cb);
+                codes8<DT, BITS, RNG, FMA>(raw[k], mn[k], sc[k], nz, cb);
 #pragma unroll
-                for (int j = 0; j < 8; j++) acc[j] |= cb[j] << (ni * BITS);
+                for (int j = 0; j < 8; j++) {
+                    if (NoOverflow<RNG>::value) acc[j] += cb[j] << (ni * BITS);      // disjoint slots: a sum is an OR
+                    else acc[j] |= cb[j] << (ni * BITS);
+                }
             }
         }
         // low bytes of the eight accumulators -> two words -> one 8-byte store

@@ -281,21 +281,37 @@ int oracle_quantize(const void *x, int dtype, int64_t n, int bits, uint64_t seed
                 case RNG_RTN:      nz = 0.5f; break;
                 default:           nz = noise[i]; break;
                 }
-                float u;
-                if (dtype != DT_F16) {
+                const int maxc = (1 << bits) - 1;
+                const int no_overflow_mode = (rng_mode == RNG_FAST || rng_mode == RNG_RTN);
+                int32_t val;
+                if (dtype == DT_BF16) {
+                    /* ours (bf16 is not a reference type): u = fma(x - min, scale, fl32(noise - 0.5)), clamped to
+                     * [0, 2^bits - 1] (NaN -> 0), then rounded to nearest even */
                     float t = xv - mn[g];
-                    u = (fma_mode || dtype == DT_BF16) ? fmaf(t, sc[g], nz) : (t * sc[g]) + nz;
+                    float nzc = nz - 0.5f;
+                    float u = fmaf(t, sc[g], nzc);
+                    float w = (u > 0.0f) ? u : 0.0f;
+                    if (w > (float)maxc) w = (float)maxc;
+                    val = float2int_rn(w);
                 } else {
-                    float t = round_T(xv - mn[g], dtype);
-                    float p = round_T(t * sc[g], dtype);
-                    u = p + nz;
+                    float u;
+                    if (dtype == DT_F32) {
+                        float t = xv - mn[g];
+                        u = fma_mode ? fmaf(t, sc[g], nz) : (t * sc[g]) + nz;
+                    } else {
+                        float t = round_T(xv - mn[g], dtype);
+                        float p = round_T(t * sc[g], dtype);
+                        u = p + nz;
+                    }
+                    /* (double)u - 0.5, compared with 0 in double, then narrowed to float for the conversion */
+                    double w = (double)u - 0.5;
+                    w = (w > 0.0) ? w : 0.0;
+                    val = float2int_rn((float)w);
+                    /* The reference has no upper clamp (a code of 2^bits spills / wraps).  The reference stream and
+                     * EXTERNAL keep that.  FAST and RTN, which are ours, cap the fp16 code at 2^bits - 1 (fp32 cannot
+                     * overflow there: the noise stays below 1). */
+                    if (dtype == DT_F16 && no_overflow_mode && val > maxc) val = maxc;
                 }
-                /* (double)u - 0.5, compared with 0 in double, then narrowed to float for the conversion */
-                double w = (double)u - 0.5;
-                w = (w > 0.0) ? w : 0.0;
-                int32_t val = float2int_rn((float)w);
-                /* fp32 / fp16 keep the reference's missing upper clamp; bf16 (ours) clamps */
-                if (dtype == DT_BF16 && val > (1 << bits) - 1) val = (1 << bits) - 1;
                 byte |= (uint8_t)((uint32_t)val << (ni * bits));   /* no upper clamp: overflow spills / wraps */
             }
             packed[gid] = byte;
