@@ -60,21 +60,13 @@ template <bool CENTRED>
 __device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& rk, float2 (&even)[4], float2 (&odd)[4]) {
     const uint4 r = philox4x32_10((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#ifdef GACT_NOISE_I2F
-    const float2 s2 = splat2(0.00390625f), o2 = splat2(CENTRED ? -0.498046875f : 0.001953125f);
-#else
-    // 2^23 + byte by byte permute, then (2^23 + b) / 256 - 2^15 + offset in one exact multiply-add
-    const float2 s2 = splat2(0.00390625f), o2 = splat2((CENTRED ? -0.498046875f : 0.001953125f) - 32768.0f);
-#endif
+    // byte -> float without a conversion: a byte permute drops it into bits 8..15 of the mantissa of 2^23, giving
+    // 2^23 + 256*b; times 2^-16 that is 128 + b/256, and the offset below brings (b + 0.5)/256 (- 0.5), all exact
+    const float2 s2 = splat2(1.52587890625e-05f), o2 = splat2((CENTRED ? -0.498046875f : 0.001953125f) - 128.0f);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-#ifdef GACT_NOISE_I2F
-        const float b0 = __uint2float_rn(w[i] & 0xffu), b1 = __uint2float_rn((w[i] >> 8) & 0xffu);
-        const float b2 = __uint2float_rn((w[i] >> 16) & 0xffu), b3 = __uint2float_rn(w[i] >> 24);
-#else
-        const float b0 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7540u)), b1 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7541u));
-        const float b2 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7542u)), b3 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7543u));
-#endif
+        const float b0 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7504u)), b1 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7514u));
+        const float b2 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7524u)), b3 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7534u));
         float2 (&dst)[4] = (i < 2) ? even : odd;
         dst[(2 * i) & 3] = fma2(make_float2(b0, b1), s2, o2);
         dst[(2 * i + 1) & 3] = fma2(make_float2(b2, b3), s2, o2);
