@@ -9,7 +9,7 @@ Workload (the kernel sweep the metric is quoted on): post-ReLU activations of sh
 widths drawn from {2,4,8}.  One step = a "forward" phase that quantizes every tensor of the set followed by a
 "backward" phase that dequantizes them in reverse order, so that nothing a kernel reads is still in L2 from the
 kernel that wrote it (the set moves ~10 GB per step; every big tensor is larger than L2).
-`value` = algorithmic bytes (read + written) of all launches of all ranks / max-over-ranks device
+`value` = algorithmic bytes (tensor + packed codes + per-group min and scale, each counted once) of all launches of all ranks / max-over-ranks device
 time, inputs resident in HBM.  `e2e` = the same bytes through the public ops (gact.ops.op_quantize /
 op_dequantize) starting from pinned host buffers and ending with the reconstructed tensors back in host memory.
 

@@ -91,6 +91,15 @@ class _NoGuard:
 _NO_GUARD = _NoGuard()
 
 
+def guard_and_stream(t: torch.Tensor):
+    """(context, cudaStream_t) for a library call on tensor t: one current-device query serves both."""
+    cur = torch.cuda.current_device()
+    idx = t.device.index
+    if idx == cur:
+        return _NO_GUARD, (_raw_stream(cur) if _raw_stream is not None else torch.cuda.current_stream().cuda_stream)
+    return torch.cuda.device(t.device), torch.cuda.current_stream(t.device).cuda_stream
+
+
 def device_guard(t: torch.Tensor):
     """Context that makes the tensor's device current for the duration of a library call.  The hooks almost
     always run with the right device already current, in which case this costs one comparison."""

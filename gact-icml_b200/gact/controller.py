@@ -64,6 +64,10 @@ class Controller:
 
         if self._hook_installed:
             return
+        if config.compress_activation:
+            # the hooks run for every saved tensor of every step: hand autograd the quantizer's bound methods
+            # directly instead of two more Python frames per call
+            pack_hook, unpack_hook = self.quantizer.quantize, self.quantizer.dequantize
         torch._C._autograd._push_saved_tensors_default_hooks(pack_hook, unpack_hook)
         self._hook_installed = True
 

@@ -245,9 +245,10 @@ def quantize_compact(input, q_bit, seed):
     G, nbytes, off_min, off_scale, total, code = _layout(n, q_bit, x.dtype)
     buf = torch.empty(total, dtype=torch.uint8, device=x.device)
     base = buf.data_ptr()
-    with nv.device_guard(x):
+    guard, stream = nv.guard_and_stream(x)
+    with guard:
         st = nv.lib.gact_quantize(x.data_ptr(), code, n, q_bit, int(seed) & 0xFFFFFFFFFFFFFFFF, nv.RNG_CODE[config.rng_mode],
-                                  None, int(config.fma), base, base + off_min, base + off_scale, nv.stream_ptr())
+                                  None, int(config.fma), base, base + off_min, base + off_scale, stream)
     global launch_count
     launch_count += 1
     if st:
@@ -262,8 +263,9 @@ def dequantize_compact(p, shape):
     else:
         out = torch.empty_strided(shape, p.strides, dtype=p.dtype, device=p.buf.device)
     base = p.buf.data_ptr()
-    with nv.device_guard(out):
-        st = nv.lib.gact_dequantize(base, base + off_min, base + off_scale, code, p.n, p.bits, out.data_ptr(), nv.stream_ptr())
+    guard, stream = nv.guard_and_stream(out)
+    with guard:
+        st = nv.lib.gact_dequantize(base, base + off_min, base + off_scale, code, p.n, p.bits, out.data_ptr(), stream)
     global launch_count
     launch_count += 1
     if st:

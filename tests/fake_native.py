@@ -102,6 +102,10 @@ class FakeNative:
     def device_guard(t):
         return contextlib.nullcontext()
 
+    @staticmethod
+    def guard_and_stream(t):
+        return contextlib.nullcontext(), 0
+
 
 def install(monkeypatch):
     """Route gact.ops / gact.autoprec / gact.quantizer to the host-memory stand-in."""
