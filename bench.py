@@ -393,6 +393,53 @@ def cpu_baseline(spec, sample_elems, reps):
                       f"CPU restatement of the reference kernels (oracle/gact_oracle.c, OpenMP), {reps} pass(es), {dt:.1f} s"}
 
 
+def reference_cuda_rows():
+    """Extra information for the reference arm: the reference's own CUDA kernels (built unmodified into
+    oracle/_ref) timed on this GPU for the fp16 cases of the sweep (the reference does not take bf16):
+    quantize = its minimax + scale + pack kernels, dequantize = its unpack kernel.  None without a GPU or binaries."""
+    if not torch.cuda.is_available():
+        return None
+    try:
+        from oracle import build_ref
+        q, m = build_ref.load("ref_quantization"), build_ref.load("ref_minimax")
+    except Exception:
+        return None
+    if q is None or m is None:
+        return None
+    dev = torch.device("cuda", 0)
+    n = 1
+    for s_ in BIG_SHAPE:
+        n *= s_
+    G = n // GROUP
+    x = torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(1234)).clamp_min_(0).half()
+    groups = x.view(G, GROUP)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = {}
+    for bits in (1, 2, 4, 8):
+        by = alg_bytes(n, bits, 2, 2)
+
+        def med(fn):
+            ts = []
+            for _ in range(5):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); r = fn(); e1.record(); torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ts.sort()
+            return ts[2], r
+
+        def quant():
+            mn, mx = m.minimax(groups)
+            return q.pack_single_precision(groups.view(G, 1, GROUP), mn.view(G, 1, 1), mx.view(G, 1, 1), bits, True, 1) + (mn,)
+
+        tq, (packed, scale, mn) = med(quant)
+        td, _ = med(lambda: q.unpack_single_precision(packed, bits, scale, mn.view(G, 1, 1), G, 1, GROUP))
+        rows[f"relu_float16_b{bits}"] = {"quantize_GBps": round(by / tq / 1e6, 1), "dequantize_GBps": round(by / td / 1e6, 1),
+                                          "quantize_us": round(tq * 1e3, 1), "dequantize_us": round(td * 1e3, 1)}
+        del packed, scale, mn
+    return rows
+
+
 def run_reference(args):
     """The reference has no CPU implementation of this path (every entry point demands CUDA tensors), so its
     arm is the CPU restatement of its kernels (the oracle), on all host threads, over a bounded sample."""
@@ -418,6 +465,9 @@ def run_reference(args):
             "config": {"workload": "kernel sweep (bounded sample on host cores)", "group_size": GROUP, "rng": "curand"},
             "cpu_baseline": base,
             "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    extra = reference_cuda_rows()
+    if extra is not None:
+        line["reference_cuda_kernels_on_this_gpu"] = extra
     print(json.dumps(line), flush=True)
 
 
