@@ -163,3 +163,33 @@ def test_argument_errors():
     assert f(x.data_ptr(), 0, 512, 2, 0, 3, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 6      # noise missing
     assert f(x.data_ptr(), 0, 0, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 0        # empty input
     torch.cuda.synchronize()
+
+
+def test_more_than_2_to_31_elements():
+    """64-bit indexing: a 4.3 GB fp16 tensor; the far end is checked against the oracle (round to nearest has no
+    index-dependent noise, so a slice that starts on a row-block boundary can be checked on its own)."""
+    from gact.ops import quantize_pack, dequantize_and_unpack
+    n = (1 << 31) + 256 * 12 + 100
+    free, _ = torch.cuda.mem_get_info()
+    if free < 14 * (1 << 30):
+        pytest.skip("not enough free device memory")
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.empty(n, dtype=torch.float16, device="cuda")
+    step = 1 << 28
+    for i in range(0, n, step):
+        x[i:i + step] = torch.randn(min(step, n - i), device="cuda", generator=g).half()
+    q, sc, mn = quantize_pack(x, 2, 0, rng_mode="rtn")
+    G = (n + 255) // 256
+    start_g = (G - 1024) // 4 * 4                        # a row-block boundary near the end
+    tail = x[start_g * 256:].cpu()
+    opk, omn, osc = oracle.quantize(tail, 2, 0, "rtn")
+    assert torch.equal(q[start_g // 4 * 256:-1].cpu().view(torch.uint8), opk)
+    assert_bits_equal(mn.reshape(-1)[start_g:], omn, "min")
+    assert_bits_equal(sc.reshape(-1)[start_g:], osc, "scale")
+    y = dequantize_and_unpack(q, (n,), 2, sc, mn)
+    want = oracle.dequantize(opk, omn, osc, tail.numel(), 2)
+    assert_bits_equal(y[start_g * 256:], want, "dequantized tail")
+    first = oracle.quantize(x[:256 * 64].cpu(), 2, 0, "rtn")[0]
+    assert torch.equal(q[:first.numel()].cpu().view(torch.uint8), first)
+    del x, y, q
+    torch.cuda.empty_cache()
