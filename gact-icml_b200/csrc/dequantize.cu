@@ -1,8 +1,8 @@
 // Unpack + dequantize: out = T(T(code) / scale) + min, written for the first n elements only.
 //
-// A warp owns a tile of GPW = max(4, wpt) groups = U row-blocks of the packed layout.  Each lane reads its 8
-// packed bytes per row-block with one 8-byte load - all loads of the
-// tile first - and writes 8 output values per group with one streaming store (16 bytes, or 32 bytes for fp32).
+// A warp owns a tile of 4, 8 or 16 groups (by tensor size, see launch_dequantize) = U row-blocks of the packed
+// layout.  Each lane reads its 8 packed bytes per row-block with one 8-byte load - all loads of the tile
+// first - and writes 8 output values per group with one streaming store (16 bytes, or 32 bytes for fp32).
 //
 // No per-element division.  The quotient code/scale is formed from one reciprocal per group:
 //   fp16:  round_h(fl32(code * fl32(1/scale))) equals round_h(fl32(code / scale)) for every half-precision
@@ -45,12 +45,13 @@ __device__ __forceinline__ void store_group8_slow(void* out, int64_t n, int64_t 
     }
 }
 
-template <int DT, int BITS>
+// TG = groups per warp tile (a 1-bit row-block holds 8, so at least that many there)
+template <int DT, int BITS, int TG>
 __global__ void __launch_bounds__(kDThreads) dequantize_kernel(const DequantArgs a) {
     using E = Elem<DT>;
     using T = typename E::T;
     constexpr int WPT = 8 / BITS;
-    constexpr int U = (WPT >= 4) ? 1 : 4 / WPT;
+    constexpr int U = (WPT >= TG) ? 1 : TG / WPT;
     constexpr int GPW = WPT * U;
     constexpr uint32_t MASK4 = ((1u << BITS) - 1u) * 0x01010101u;
     const int lane = threadIdx.x & 31;
@@ -162,15 +163,27 @@ __global__ void __launch_bounds__(kDThreads) dequantize_kernel(const DequantArgs
     }
 }
 
-template <int DT, int BITS> static int launch_dequantize(const DequantArgs& a, cudaStream_t s) {
+template <int DT, int BITS, int TG> static int launch_dequantize_tile(const DequantArgs& a, cudaStream_t s) {
     constexpr int WPT = 8 / BITS;
-    constexpr int U = (WPT >= 4) ? 1 : 4 / WPT;
+    constexpr int U = (WPT >= TG) ? 1 : TG / WPT;
     const int64_t tiles = (a.R + U - 1) / U;
     const int64_t want = (tiles + kDThreads / 32 - 1) / (kDThreads / 32);
     const int64_t cap = (int64_t)kSMs * 16;
     const int blocks = (int)(want < cap ? want : cap);
-    dequantize_kernel<DT, BITS><<<blocks, kDThreads, 0, s>>>(a);
+    dequantize_kernel<DT, BITS, TG><<<blocks, kDThreads, 0, s>>>(a);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+}
+
+// Tile size by tensor size (measured): large tiles amortise the per-tile work (scale / min fetch, reciprocal,
+// broadcasts) and keep more loads in flight, but a tensor must still spread over enough warps to fill the GPU:
+// 16 groups per warp (8 for fp32, whose stores are twice as wide) once that leaves half a resident wave of warps,
+// else 8, else 4.
+template <int DT, int BITS> static int launch_dequantize(const DequantArgs& a, cudaStream_t s) {
+    constexpr int64_t kHalfWave = (int64_t)kSMs * 32;         // warps: half of 148 SMs x 64 resident warps
+    constexpr int kBig = (DT == GACT_F32) ? 8 : 16;
+    if (a.G >= kBig * kHalfWave) return launch_dequantize_tile<DT, BITS, kBig>(a, s);
+    if (kBig > 8 && a.G >= 8 * kHalfWave) return launch_dequantize_tile<DT, BITS, 8>(a, s);
+    return launch_dequantize_tile<DT, BITS, 4>(a, s);
 }
 
 template <int DT> static int dispatch_dq(const DequantArgs& a, int bits, cudaStream_t s) {
