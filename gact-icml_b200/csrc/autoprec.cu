@@ -1,6 +1,9 @@
 // Device side of the auto-precision controller: squared distances between gradient vectors, the
 // sensitivity clamp, and the greedy bit allocation.
+#include <algorithm>
+#include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "gact_common.cuh"
 
@@ -120,9 +123,9 @@ __global__ void sensitivity_kernel(const double* d3, double scale, float* C, int
 // ---------------------------------------------------------------------------------------------------
 constexpr int kPThreads = 1024;
 
-__device__ __forceinline__ int next_bits(int b) { return b == 32 ? 8 : b == 8 ? 4 : b == 4 ? 2 : b == 2 ? 1 : 0; }
+__host__ __device__ __forceinline__ int next_bits(int b) { return b == 32 ? 8 : b == 8 ? 4 : b == 4 ? 2 : b == 2 ? 1 : 0; }
 
-__device__ __forceinline__ double step_gain(float C, int b) {
+__host__ __device__ __forceinline__ double step_gain(float C, int b) {
     const int nb = next_bits(b);
     const int c2 = ((1 << nb) - 1) * ((1 << nb) - 1);
     if (b == 32) return -(double)C / c2;
@@ -130,11 +133,16 @@ __device__ __forceinline__ double step_gain(float C, int b) {
     return C * (1.0 / c1 - 1.0 / c2);
 }
 
-__device__ __forceinline__ uint64_t make_candidate(float C, int b, int64_t w, int idx) {
+__host__ __device__ __forceinline__ uint64_t make_candidate(float C, int b, int64_t w, int idx) {
     const int db = b - next_bits(b);
     float key = (float)(step_gain(C, b) / (double)(w * db));
     if (key == 0.0f) key = 0.0f;                                  // -0 and +0 compare equal in the reference
+#ifdef __CUDA_ARCH__
     uint32_t u = __float_as_uint(key);
+#else
+    uint32_t u;
+    memcpy(&u, &key, sizeof u);
+#endif
     u ^= (u >> 31) ? 0xffffffffu : 0x80000000u;                   // order-preserving map to unsigned
     return ((uint64_t)u << 32) | (uint32_t)idx;
 }
@@ -149,7 +157,7 @@ __global__ void __launch_bounds__(kPThreads) calc_precision_kernel(int32_t* __re
     double part = 0;
     for (int i = tid; i < L; i += kPThreads) {
         const int bi = b[i];
-        if (bi > 1) {
+        if (bi > 1) {                                             // entries already at 1 bit are not counted (as in the reference)
             cand[i] = make_candidate(C[i], bi, w[i], i);
             part += (double)((int64_t)bi * w[i]);                 // integer-valued: the order of the sum is immaterial
         } else {
@@ -309,6 +317,38 @@ extern "C" int gact_calc_precision(int32_t* b, const float* C, const int64_t* w,
     }
     calc_precision_kernel<<<1, kPThreads, smem, (cudaStream_t)stream>>>(b, C, w, L, target, status);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+}
+
+// Host twin of the kernel above for callers that hold b, C and w in host memory (the reference's calc_precision
+// takes CPU tensors): same keys, same pop order (a max-heap of the 64-bit candidates), same stopping rule.
+extern "C" int gact_calc_precision_host(int32_t* b, const float* C, const int64_t* w, int L, double target) {
+    if (L < 0) return GACT_ERR_SIZE;
+    if (L == 0) return GACT_OK;
+    if (!b || !C || !w) return GACT_ERR_NULL;
+    std::vector<uint64_t> heap;
+    heap.reserve((size_t)L);
+    double b_sum = 0;
+    for (int i = 0; i < L; i++) {
+        if (b[i] > 1) {                                           // entries already at 1 bit are not counted (as in the reference)
+            b_sum += (double)((int64_t)b[i] * w[i]);
+            heap.push_back(make_candidate(C[i], b[i], w[i], i));
+        }
+    }
+    std::make_heap(heap.begin(), heap.end());
+    while (b_sum > target) {
+        if (heap.empty()) return GACT_ERR_BUDGET;
+        std::pop_heap(heap.begin(), heap.end());
+        const int i = (int)(uint32_t)heap.back();
+        heap.pop_back();
+        const int nb = next_bits(b[i]);
+        b_sum -= (double)(w[i] * (b[i] - nb));
+        b[i] = nb;
+        if (nb > 1) {
+            heap.push_back(make_candidate(C[i], nb, w[i], i));
+            std::push_heap(heap.begin(), heap.end());
+        }
+    }
+    return GACT_OK;
 }
 
 extern "C" int gact_version(void) { return 100; }

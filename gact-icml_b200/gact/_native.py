@@ -43,6 +43,7 @@ _SIGNATURES = {
     "gact_sq_diffs3_noalloc": ([_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _vp], _i),
     "gact_sensitivity": ([_vp, _d, _vp, _i, _vp], _i),
     "gact_calc_precision": ([_vp, _vp, _vp, _i, _d, _vp, _vp], _i),
+    "gact_calc_precision_host": ([_vp, _vp, _vp, _i, _d], _i),
 }
 for _name, (_args, _res) in _SIGNATURES.items():
     _fn = getattr(lib, _name)

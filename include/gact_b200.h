@@ -179,6 +179,13 @@ int gact_sensitivity(const double* d3, double scale, float* C, int L, void* stre
 int gact_calc_precision(int32_t* b, const float* C, const int64_t* w, int L, double target, int* status,
                         void* stream);
 
+/*
+ * The same allocation on host arrays (no GPU involved), for callers that keep b, C and w in host memory as
+ * the reference's calc_precision() does (calc_precision.cc:66 takes CPU tensors).  Returns GACT_OK or
+ * GACT_ERR_BUDGET.
+ */
+int gact_calc_precision_host(int32_t* b, const float* C, const int64_t* w, int L, double target);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,3 +79,38 @@ def test_import_fails_loudly_without_the_library(tmp_path, monkeypatch):
         assert "no fallback" in str(e)
     else:
         raise AssertionError("importing the binding next to no library must raise")
+
+
+def test_calc_precision_host_twin(golden_dir=None):
+    """gact_calc_precision_host (no GPU involved) through the pybind-compatible shim: the recorded outputs of the
+    reference's calc_precision.cc, random cases against the oracle, the 1-bit-entries case, and the unreachable budget."""
+    import json
+    import numpy as np
+    import pytest
+    import torch
+    import oracle
+    from gact.cpp_extension.calc_precision import calc_precision
+    cases = json.loads((ROOT / "tests" / "golden" / "calc_precision.json").read_text())["cases"]
+    for c in cases:
+        C = torch.from_numpy(np.array(c["C_bits"], dtype=np.uint32).view(np.float32).copy())
+        w = torch.tensor(c["w"], dtype=torch.int64)
+        b = torch.full((len(c["w"]),), c["start"], dtype=torch.int32)
+        out = calc_precision(b, C, w, c["target"])
+        assert out is b and out.tolist() == c["bits"]
+    g = torch.Generator().manual_seed(7)
+    for L in (1, 2, 17, 300, 2000):
+        C = torch.rand(L, generator=g) * torch.tensor(10.0) ** torch.randint(-6, 6, (L,), generator=g)
+        C[::7] = C[0]                                              # equal keys: larger index first
+        w = torch.randint(1, 1 << 20, (L,), generator=g, dtype=torch.int64)
+        start = torch.tensor([32, 8, 4, 2, 1], dtype=torch.int32)[torch.randint(0, 5, (L,), generator=g)]
+        for avg in (1.0, 1.5, 3.0, 7.9):
+            target = avg * float(w.sum())
+            want, st = oracle.calc_precision(start.clone(), C, w, target)
+            if st:
+                continue
+            got = calc_precision(start.clone(), C, w, target)
+            assert torch.equal(got, want), (L, avg)
+    with pytest.raises(RuntimeError):
+        calc_precision(torch.full((4,), 32, dtype=torch.int32), torch.ones(4), torch.full((4,), 256, dtype=torch.int64), 100.0)
+    with pytest.raises(RuntimeError):
+        calc_precision(torch.full((4,), 32, dtype=torch.int64), torch.ones(4), torch.full((4,), 256, dtype=torch.int64), 1e9)

@@ -107,3 +107,22 @@ def test_calc_precision_large_and_unreachable():
     # a budget below one bit per element cannot be met: every tensor ends at 1 bit and the status says so
     got, status = gpu_calc_precision(b, C, w, 0.5 * float(w.sum()))
     assert set(got.tolist()) == {1} and status == 8
+
+
+def test_calc_precision_mixed_starting_widths():
+    """Starting widths other than 32, entries already at 1 bit included (the reference leaves those out of the
+    budget sum, calc_precision.cc:96-101), against the oracle and the host twin."""
+    from gact.cpp_extension.calc_precision import calc_precision as host_calc_precision
+    g = torch.Generator().manual_seed(11)
+    for L in (5, 64, 1500):
+        C = torch.rand(L, generator=g) * 50
+        C[::9] = 2.0
+        w = torch.randint(1, 1 << 18, (L,), generator=g, dtype=torch.int64)
+        start = torch.tensor([32, 8, 4, 2, 1], dtype=torch.int32)[torch.randint(0, 5, (L,), generator=g)]
+        for avg in (1.0, 2.5, 6.0):
+            target = avg * float(w.sum())
+            want, ost = oracle.calc_precision(start.clone(), C, w, target)
+            got, status = gpu_calc_precision(start.clone(), C, w, target)
+            assert got.tolist() == want.tolist() and (status != 0) == (ost != 0)
+            if ost == 0:
+                assert torch.equal(host_calc_precision(start.clone(), C, w, target), want)

@@ -72,3 +72,60 @@ def test_mask_against_reference_kernels(ref):
         rout = q.act_dequantize_dropout_mask(rmask, n)
         assert torch.equal(op_dequantize_mask([ours, x.shape]), rout)
         assert torch.equal(rout, x)
+
+
+def _reference_style_quantize(ext_minimax, ext_quantization, x, q_bit, seed):
+    """The data flow of the reference's op_quantize / op_dequantize (pad, group, minimax, pack; unpack, slice),
+    written against whatever modules are passed in."""
+    n = x.numel()
+    G = (n + 255) // 256
+    flat = x.reshape(1, -1)
+    if G * 256 > n:
+        flat = torch.cat([flat, torch.zeros([1, G * 256 - n], dtype=x.dtype, device=x.device)], dim=1)
+    groups = flat.reshape(-1, 256)
+    q_min, mx = ext_minimax.minimax(groups)
+    q_min = q_min.reshape(G, -1, 1)
+    q_input, q_scale = ext_quantization.pack_single_precision(groups.view(G, -1, 256), q_min, mx.view(G, -1, 1), q_bit, True, seed)
+    out = ext_quantization.unpack_single_precision(q_input, q_bit, q_scale, q_min, G, 1, 256)
+    return q_input, q_scale, q_min, out.ravel()[:n].reshape(x.shape).contiguous()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+def test_pybind_compatible_shims_against_reference_modules(ref, dtype, bits):
+    """gact.cpp_extension.{minimax,quantization} are drop-ins for the reference's modules of the same names: the same
+    Python, run once on the reference's modules and once on the shims, gives the same tensors."""
+    import gact.cpp_extension.minimax as shim_minimax
+    import gact.cpp_extension.quantization as shim_quantization
+    rq, rm = ref
+    for shape, seed in (((24, 256), 0), ((37, 300), 5), ((8, 17, 33), 77)):
+        x = torch.randn(shape, device="cuda").to(dtype)
+        a = _reference_style_quantize(rm, rq, x, bits, seed)
+        b = _reference_style_quantize(shim_minimax, shim_quantization, x, bits, seed)
+        assert a[0].shape == b[0].shape and a[0].dtype == b[0].dtype
+        assert torch.equal(a[0][:-1], b[0][:-1])                   # the last byte is unspecified on both sides
+        for i, what in ((1, "scale"), (2, "min"), (3, "dequantized")):
+            assert a[i].shape == b[i].shape and a[i].dtype == b[i].dtype, what
+            assert_bits_equal(b[i].reshape(-1), a[i].reshape(-1), f"{what} {dtype} b={bits} {shape}")
+    m = (torch.rand(512 * 9, device="cuda") < 0.3).to(torch.uint8)
+    assert torch.equal(shim_quantization.act_quantize_dropout_mask(m), rq.act_quantize_dropout_mask(m))
+    w = shim_quantization.act_quantize_dropout_mask(m)
+    assert torch.equal(shim_quantization.act_dequantize_dropout_mask(w, m.numel()), m)
+
+
+def test_calc_precision_shim_against_reference_module():
+    """The CPU-side greedy allocator of the reference (built unmodified) against gact.cpp_extension.calc_precision."""
+    rc = build_ref.load("ref_calc_precision")
+    if rc is None:
+        pytest.skip("oracle/_ref not built")
+    from gact.cpp_extension.calc_precision import calc_precision
+    g = torch.Generator().manual_seed(3)
+    for L in (3, 50, 700):
+        C = torch.rand(L, generator=g) * 100
+        C[::5] = 1.0
+        w = torch.randint(1, 1 << 22, (L,), generator=g, dtype=torch.int64)
+        for avg in (1.2, 2.0, 4.0, 6.5):
+            target = avg * float(w.sum())
+            want = rc.calc_precision(torch.full((L,), 32, dtype=torch.int32), C, w, target)
+            got = calc_precision(torch.full((L,), 32, dtype=torch.int32), C, w, target)
+            assert torch.equal(got, want), (L, avg)
