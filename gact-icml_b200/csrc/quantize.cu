@@ -13,6 +13,8 @@
 // mantissa bits; the bits above it fall off when the byte is cut out.  fp16 follows the reference's
 // half-precision arithmetic with two-wide subtract / multiply; NaN products become 0 with a two-wide max, which
 // is what the reference's `max(., 0)` does to them.
+#include <atomic>
+
 #include "gact_common.cuh"
 
 namespace gact {
@@ -417,6 +419,9 @@ __global__ void __launch_bounds__(kPipeThreads, GACT_PIPE_MINB) quantize_pipe_ke
     }
 }
 
+// smallest number of whole chunks for which the ring kernel is used (see launch_quantize); gact_set_ring_min_chunks
+static std::atomic<int64_t> g_ring_min_chunks{1536};
+
 template <int DT, int BITS, int RNG, bool FMA>
 static int launch_quantize(const QuantArgs& args, cudaStream_t s) {
     constexpr int GPW = Tile<DT, BITS>::GPW;
@@ -431,9 +436,11 @@ static int launch_quantize(const QuantArgs& args, cudaStream_t s) {
     }
     a.tile_begin = 0;
     // Measured: the ring pays off where the tile routine is long (16-bit inputs with generated noise); fp32 inputs and
-    // round-to-nearest run faster from direct loads.
+    // round-to-nearest run faster from direct loads.  So do tensors of less than ~48 MB: with only a few chunks per
+    // CTA the ring's whole-chunk granularity leaves SMs unevenly loaded, while the direct-load kernel spreads single
+    // tiles (33 MB bf16: 18.4 us direct vs 20.5 us ring; 67 MB: 30.7 vs 28.7).
     constexpr bool kUsePipe = (DT != GACT_F32) && (RNG != GACT_RNG_RTN);
-    if (kUsePipe && nchunks > 0 && pipe_ready == 1) {
+    if (kUsePipe && nchunks >= g_ring_min_chunks.load(std::memory_order_relaxed) && pipe_ready == 1) {
         static int pipe_resident = 0;
         if (pipe_resident == 0) {
             int per_sm = 0;
@@ -562,6 +569,11 @@ extern "C" int gact_pipeline_error(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_pipeline_error, sizeof(int)) != cudaSuccess) return -1;
     return v;
+}
+
+extern "C" int64_t gact_set_ring_min_chunks(int64_t min_chunks) {
+    if (min_chunks < 1) return g_ring_min_chunks.load(std::memory_order_relaxed);
+    return g_ring_min_chunks.exchange(min_chunks, std::memory_order_relaxed);
 }
 
 extern "C" int gact_minimax(const void* x, int dtype, int64_t n, void* mn, void* mx, void* stream) {

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "gact_sensitivity": ([_vp, _d, _vp, _i, _vp], _i),
     "gact_calc_precision": ([_vp, _vp, _vp, _i, _d, _vp, _vp], _i),
     "gact_calc_precision_host": ([_vp, _vp, _vp, _i, _d], _i),
+    "gact_set_ring_min_chunks": ([_i64], _i64),
 }
 for _name, (_args, _res) in _SIGNATURES.items():
     _fn = getattr(lib, _name)

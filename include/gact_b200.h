@@ -84,6 +84,14 @@ int gact_quantize(const void* x, int dtype, int64_t n, int bits, uint64_t seed, 
 int gact_pipeline_error(void);
 
 /*
+ * Tuning knob without a reference counterpart: gact_quantize runs 16-bit inputs with generated noise through
+ * its bulk-copy ring kernel when the tensor holds at least `min_chunks` whole 32 KB chunks (default 1536, i.e.
+ * 48 MB), and through the direct-load kernel otherwise; both give the same bytes.  Returns the previous value;
+ * min_chunks < 1 only reads it.  Process-wide; tests lower it to push small cases through the ring.
+ */
+int64_t gact_set_ring_min_chunks(int64_t min_chunks);
+
+/*
  * Unpack + dequantize: out[i] = T(T(code)/scale) + min for the first n elements (bf16, not a reference type:
  * bf16(fma(code, fl32(1/scale), min)) with the fp32 qscale written by gact_quantize).
  * Replaces unpack_single_precision() (gact/gact/cpp_extension/quantization.cc:36-49,

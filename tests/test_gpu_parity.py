@@ -11,6 +11,19 @@ from helpers import abi_dequantize, abi_quantize, assert_bits_equal
 
 pytestmark = pytest.mark.gpu
 
+
+
+@pytest.fixture(autouse=True, params=["ring", "default"])
+def ring_threshold(request):
+    """Every test of this module runs twice: with the ring kernel taking every tensor of at least one 32 KB chunk,
+    and with the library's own choice (ring from 48 MB on, direct loads below)."""
+    from gact import _native as nv
+    before = nv.lib.gact_set_ring_min_chunks(1 if request.param == "ring" else 0)
+    yield request.param
+    nv.lib.gact_set_ring_min_chunks(before)
+    assert nv.lib.gact_pipeline_error() == 0
+
+
 DTYPES = [torch.float32, torch.float16, torch.bfloat16]
 BITS = [1, 2, 4, 8]
 # sizes: single element, around one group, ragged (n % 256 != 0), G % wpt != 0 for every width, several tiles
@@ -165,9 +178,11 @@ def test_argument_errors():
     torch.cuda.synchronize()
 
 
-def test_more_than_2_to_31_elements():
+def test_more_than_2_to_31_elements(ring_threshold):
     """64-bit indexing: a 4.3 GB fp16 tensor; the far end is checked against the oracle (round to nearest has no
     index-dependent noise, so a slice that starts on a row-block boundary can be checked on its own)."""
+    if ring_threshold == "ring":
+        pytest.skip("round to nearest never takes the ring kernel")
     from gact.ops import quantize_pack, dequantize_and_unpack
     n = (1 << 31) + 256 * 12 + 100
     free, _ = torch.cuda.mem_get_info()
@@ -193,3 +208,16 @@ def test_more_than_2_to_31_elements():
     assert torch.equal(q[:first.numel()].cpu().view(torch.uint8), first)
     del x, y, q
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", BITS)
+def test_above_the_ring_threshold(dtype, bits, ring_threshold):
+    """50 MB tensors: the size from which the library picks the ring kernel by itself, plus a ragged tail."""
+    if ring_threshold == "ring":
+        pytest.skip("same kernel either way at this size")
+    n = 1536 * 16384 + 3 * 16384 + 1000
+    x = make_input("relu", n, dtype, seed=bits)
+    check_case(x, bits, 5, "fast")
+    if bits in (2, 8):
+        check_case(x, bits, 5, "curand")
