@@ -35,14 +35,14 @@ struct QuantArgs {
     PhiloxKeys rk;
 };
 
-#ifndef GACT_GPW16
-#define GACT_GPW16 8
-#endif
-template <int DT, int BITS> struct Tile {
+// Tile of one warp: TG groups (at least one row-block, i.e. 8 / BITS groups).  16-bit inputs use 8 groups per
+// tile for large tensors and 4 for small ones (shorter per-tile latency, finer spread over the SMs); fp32 uses 4.
+template <int DT, int BITS, int TG> struct Tile {
     static constexpr int WPT = 8 / BITS;
-    static constexpr int GPW = (DT == GACT_F32) ? (WPT > 4 ? WPT : 4) : (WPT > GACT_GPW16 ? WPT : GACT_GPW16);
+    static constexpr int GPW = WPT > TG ? WPT : TG;
     static constexpr int U = GPW / WPT;
 };
+template <int DT> struct BigTile { static constexpr int value = (DT == GACT_F32) ? 4 : 8; };
 
 // Which noise values reach codes8 "centred" (noise - 0.5 instead of noise).  With the 8-bit noise of FAST and the
 // constant noise of RTN, and p a half-precision value, p + noise is exact in fp32, so (p + noise) - 0.5 equals
@@ -139,10 +139,10 @@ __device__ __forceinline__ void codes8(const uint32_t (&raw)[RawRegs<DT>::N], fl
 
 // All loads of one tile (issued back to back, nothing waits on them here).  FULL: every group of the tile
 // exists and is complete, so no bounds are tested.
-template <int DT, int BITS, bool FULL>
+template <int DT, int BITS, int TG, bool FULL>
 __device__ __forceinline__ void load_tile(const QuantArgs& a, int64_t tile, int lane,
-                                          uint32_t (&raw)[Tile<DT, BITS>::GPW][RawRegs<DT>::N]) {
-    constexpr int GPW = Tile<DT, BITS>::GPW, NR = RawRegs<DT>::N;
+                                          uint32_t (&raw)[Tile<DT, BITS, TG>::GPW][RawRegs<DT>::N]) {
+    constexpr int GPW = Tile<DT, BITS, TG>::GPW, NR = RawRegs<DT>::N;
     const int64_t g0 = tile * GPW;
 #pragma unroll
     for (int k = 0; k < GPW; k++) {
@@ -158,12 +158,12 @@ __device__ __forceinline__ void load_tile(const QuantArgs& a, int64_t tile, int 
 }
 
 // min/max, scale, codes and stores of one tile whose values are already in registers
-template <int DT, int BITS, int RNG, bool FMA, bool FULL>
+template <int DT, int BITS, int RNG, bool FMA, int TG, bool FULL>
 __device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, int lane,
-                                             const uint32_t (&raw)[Tile<DT, BITS>::GPW][RawRegs<DT>::N]) {
+                                             const uint32_t (&raw)[Tile<DT, BITS, TG>::GPW][RawRegs<DT>::N]) {
     using E = Elem<DT>;
     using T = typename E::T;
-    constexpr int WPT = Tile<DT, BITS>::WPT, GPW = Tile<DT, BITS>::GPW, U = Tile<DT, BITS>::U;
+    constexpr int WPT = Tile<DT, BITS, TG>::WPT, GPW = Tile<DT, BITS, TG>::GPW, U = Tile<DT, BITS, TG>::U;
     const int64_t g0 = tile * GPW;
 
     // min / max of every group; lane k keeps group k's pair and computes its scale
@@ -275,9 +275,9 @@ __device__ __forceinline__ void process_tile(const QuantArgs& a, int64_t tile, i
 #define GACT_QMINB 3
 #endif
 
-template <int DT, int BITS, int RNG, bool FMA>
+template <int DT, int BITS, int RNG, bool FMA, int TG>
 __global__ void __launch_bounds__(kQThreads, GACT_QMINB) quantize_kernel(const __grid_constant__ QuantArgs a) {
-    constexpr int GPW = Tile<DT, BITS>::GPW, NR = RawRegs<DT>::N;
+    constexpr int GPW = Tile<DT, BITS, TG>::GPW, NR = RawRegs<DT>::N;
     const int lane = threadIdx.x & 31;
     const int64_t nwarps = (int64_t)gridDim.x * (kQThreads / 32);
     const int64_t tiles = (a.G + GPW - 1) / GPW;
@@ -285,11 +285,11 @@ __global__ void __launch_bounds__(kQThreads, GACT_QMINB) quantize_kernel(const _
     for (int64_t tile = a.tile_begin + (int64_t)blockIdx.x * (kQThreads / 32) + (threadIdx.x >> 5); tile < tiles; tile += nwarps) {
         uint32_t raw[GPW][NR];
         if (tile < full_tiles) {
-            load_tile<DT, BITS, true>(a, tile, lane, raw);
-            process_tile<DT, BITS, RNG, FMA, true>(a, tile, lane, raw);
+            load_tile<DT, BITS, TG, true>(a, tile, lane, raw);
+            process_tile<DT, BITS, RNG, FMA, TG, true>(a, tile, lane, raw);
         } else {
-            load_tile<DT, BITS, false>(a, tile, lane, raw);
-            process_tile<DT, BITS, RNG, FMA, false>(a, tile, lane, raw);
+            load_tile<DT, BITS, TG, false>(a, tile, lane, raw);
+            process_tile<DT, BITS, RNG, FMA, TG, false>(a, tile, lane, raw);
         }
     }
 }
@@ -314,7 +314,7 @@ constexpr uint32_t kWaitLimit = 1u << 20;
 #define GACT_PIPE_MINB 2
 #endif
 template <int DT, int BITS> struct Pipe {
-    static constexpr int kChunkBytes = kPipeWarps * Tile<DT, BITS>::GPW * kGroup * Elem<DT>::kBytes;
+    static constexpr int kChunkBytes = kPipeWarps * Tile<DT, BITS, BigTile<DT>::value>::GPW * kGroup * Elem<DT>::kBytes;
     static constexpr int kStages = kChunkBytes <= 32 * 1024 ? GACT_PIPE_STAGES : 2;
 };
 
@@ -347,7 +347,8 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 template <int DT, int BITS, int RNG, bool FMA>
 __global__ void __launch_bounds__(kPipeThreads, GACT_PIPE_MINB) quantize_pipe_kernel(const __grid_constant__ QuantArgs a, int64_t nchunks) {
-    constexpr int GPW = Tile<DT, BITS>::GPW, NR = RawRegs<DT>::N;
+    constexpr int TG = BigTile<DT>::value;
+    constexpr int GPW = Tile<DT, BITS, TG>::GPW, NR = RawRegs<DT>::N;
     constexpr int kChunkBytes = Pipe<DT, BITS>::kChunkBytes, kPipeStages = Pipe<DT, BITS>::kStages;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[2 * kPipeStages];       // [0..S) full, [S..2S) empty
@@ -415,64 +416,75 @@ __global__ void __launch_bounds__(kPipeThreads, GACT_PIPE_MINB) quantize_pipe_ke
         __threadfence_block();                                       // this lane's reads of the stage are done
         __syncwarp();
         if (lane == 0) mbar_arrive(bar0 + 8 * (kPipeStages + s));    // the stage may be refilled
-        process_tile<DT, BITS, RNG, FMA, true>(a, c * kPipeWarps + warp, lane, raw);
+        process_tile<DT, BITS, RNG, FMA, TG, true>(a, c * kPipeWarps + warp, lane, raw);
     }
 }
 
 // smallest number of whole chunks for which the ring kernel is used (see launch_quantize); gact_set_ring_min_chunks
 static std::atomic<int64_t> g_ring_min_chunks{1536};
+constexpr int64_t kSmallTileMaxGroups = 40960;      // 16-bit tensors of up to 20 MB take tiles of 4 groups
+
+// direct-load kernel over the tiles from a.tile_begin on (in tiles of TG groups)
+template <int DT, int BITS, int RNG, bool FMA, int TG>
+static int launch_plain(const QuantArgs& a, cudaStream_t s) {
+    constexpr int GPW = Tile<DT, BITS, TG>::GPW;
+    const int64_t tiles = (a.G + GPW - 1) / GPW - a.tile_begin;
+    if (tiles <= 0) return GACT_OK;
+    static int resident = 0;
+    if (resident == 0) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_kernel<DT, BITS, RNG, FMA, TG>, kQThreads, 0) != cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        resident = per_sm * kSMs;
+    }
+    const int64_t want = (tiles + kQThreads / 32 - 1) / (kQThreads / 32);
+    const int blocks = (int)(want < resident ? want : resident);
+    quantize_kernel<DT, BITS, RNG, FMA, TG><<<blocks, kQThreads, 0, s>>>(a);
+    return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+}
 
 template <int DT, int BITS, int RNG, bool FMA>
 static int launch_quantize(const QuantArgs& args, cudaStream_t s) {
-    constexpr int GPW = Tile<DT, BITS>::GPW;
+    constexpr int kBig = BigTile<DT>::value;
     constexpr int kChunkBytes = Pipe<DT, BITS>::kChunkBytes, kPipeStages = Pipe<DT, BITS>::kStages;
     QuantArgs a = args;
-    // ---- bulk-copy pipeline over the whole 32 KB chunks (needs 16-byte aligned input, which the ABI demands)
-    const int64_t nchunks = a.n / (kChunkBytes / Elem<DT>::kBytes);
-    static int pipe_ready = 0;          // 0 = not set up, 1 = usable, -1 = shared memory opt-in refused
-    if (pipe_ready == 0) {
-        pipe_ready = cudaFuncSetAttribute(quantize_pipe_kernel<DT, BITS, RNG, FMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          kPipeStages * kChunkBytes) == cudaSuccess ? 1 : -1;
-    }
     a.tile_begin = 0;
-    // Measured: the ring pays off where the tile routine is long (16-bit inputs with generated noise); fp32 inputs and
-    // round-to-nearest run faster from direct loads.  So do tensors of less than ~48 MB: with only a few chunks per
-    // CTA the ring's whole-chunk granularity leaves SMs unevenly loaded, while the direct-load kernel spreads single
-    // tiles (33 MB bf16: 18.4 us direct vs 20.5 us ring; 67 MB: 30.7 vs 28.7).
+    // Which kernel (all measured).  The bulk-copy ring pays off where the tile routine is long (16-bit inputs with
+    // generated noise) and the tensor is large: with only a few chunks per CTA its whole-chunk granularity leaves
+    // SMs unevenly loaded (33 MB bf16: 18.4 us direct vs 20.5 us ring; 67 MB: 30.7 vs 28.7).  fp32 inputs,
+    // round-to-nearest and everything below ~48 MB run from direct loads, 16-bit tensors of up to 20 MB with tiles
+    // of 4 groups instead of 8: the shorter tile brings a 16 MB launch from 8.9 to 7.7 us and a 1 MB one from 3.5 to 2.8.
     constexpr bool kUsePipe = (DT != GACT_F32) && (RNG != GACT_RNG_RTN);
-    if (kUsePipe && nchunks >= g_ring_min_chunks.load(std::memory_order_relaxed) && pipe_ready == 1) {
-        static int pipe_resident = 0;
-        if (pipe_resident == 0) {
-            int per_sm = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_pipe_kernel<DT, BITS, RNG, FMA>, kPipeThreads,
-                                                              kPipeStages * kChunkBytes) != cudaSuccess || per_sm < 1)
-                per_sm = 1;
-            pipe_resident = per_sm * kSMs;
+    if constexpr (kUsePipe) {
+        const int64_t nchunks = a.n / (kChunkBytes / Elem<DT>::kBytes);
+        static int pipe_ready = 0;          // 0 = not set up, 1 = usable, -1 = shared memory opt-in refused
+        if (pipe_ready == 0) {
+            pipe_ready = cudaFuncSetAttribute(quantize_pipe_kernel<DT, BITS, RNG, FMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              kPipeStages * kChunkBytes) == cudaSuccess ? 1 : -1;
         }
-        // one resident wave, with the chunks spread evenly: every CTA gets the same number of chunks (+-1)
-        const int64_t cap = pipe_resident;
-        const int64_t rounds = (nchunks + cap - 1) / cap;
-        const int blocks = (int)((nchunks + rounds - 1) / rounds);
-        quantize_pipe_kernel<DT, BITS, RNG, FMA><<<blocks, kPipeThreads, kPipeStages * kChunkBytes, s>>>(a, nchunks);
-        if (cudaGetLastError() != cudaSuccess) return GACT_ERR_LAUNCH;
-        a.tile_begin = nchunks * kPipeWarps;
-    }
-    // ---- plain kernel for what is left (less than one chunk, or everything if the pipeline is unavailable)
-    const int64_t tiles = (a.G + GPW - 1) / GPW - a.tile_begin;
-    if (tiles > 0) {
-        static int resident = 0;
-        if (resident == 0) {
-            int per_sm = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_kernel<DT, BITS, RNG, FMA>, kQThreads, 0) != cudaSuccess || per_sm < 1)
-                per_sm = 1;
-            resident = per_sm * kSMs;
+        if (nchunks >= g_ring_min_chunks.load(std::memory_order_relaxed) && pipe_ready == 1) {
+            static int pipe_resident = 0;
+            if (pipe_resident == 0) {
+                int per_sm = 0;
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_pipe_kernel<DT, BITS, RNG, FMA>, kPipeThreads,
+                                                                  kPipeStages * kChunkBytes) != cudaSuccess || per_sm < 1)
+                    per_sm = 1;
+                pipe_resident = per_sm * kSMs;
+            }
+            // one resident wave, with the chunks spread evenly: every CTA gets the same number of chunks (+-1)
+            const int64_t cap = pipe_resident;
+            const int64_t rounds = (nchunks + cap - 1) / cap;
+            const int blocks = (int)((nchunks + rounds - 1) / rounds);
+            quantize_pipe_kernel<DT, BITS, RNG, FMA><<<blocks, kPipeThreads, kPipeStages * kChunkBytes, s>>>(a, nchunks);
+            if (cudaGetLastError() != cudaSuccess) return GACT_ERR_LAUNCH;
+            a.tile_begin = nchunks * kPipeWarps;
+            return launch_plain<DT, BITS, RNG, FMA, kBig>(a, s);         // what is left: less than one chunk
         }
-        const int64_t want = (tiles + kQThreads / 32 - 1) / (kQThreads / 32);
-        const int blocks = (int)(want < resident ? want : resident);
-        quantize_kernel<DT, BITS, RNG, FMA><<<blocks, kQThreads, 0, s>>>(a);
-        if (cudaGetLastError() != cudaSuccess) return GACT_ERR_LAUNCH;
     }
-    return GACT_OK;
+    if constexpr (DT != GACT_F32 && BITS > 1) {
+        if (a.G <= kSmallTileMaxGroups) return launch_plain<DT, BITS, RNG, FMA, 4>(a, s);
+    }
+    return launch_plain<DT, BITS, RNG, FMA, kBig>(a, s);
 }
 
 template <int DT, int BITS>

@@ -140,9 +140,12 @@ def test_config1_single_tensor_round_trip():
 
 def test_many_row_blocks_grid_stride():
     """More tiles than the launch has warps, so every warp loops."""
-    x = make_input("relu", 256 * 40000 + 77, torch.float16, seed=2)
+    x = make_input("relu", 256 * 40000 + 77, torch.float16, seed=2)     # 16-bit, up to 40 960 groups: tiles of 4 groups
     check_case(x, 8, 3, "curand")
     check_case(x, 1, 3, "curand")
+    x = make_input("relu", 256 * 50000 + 77, torch.float16, seed=3)     # above that: tiles of 8 groups
+    check_case(x, 4, 3, "curand")
+    check_case(x.to(torch.bfloat16), 2, 3, "fast")
 
 
 def test_minimax_entry_point():
