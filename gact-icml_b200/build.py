@@ -55,7 +55,27 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if force or jobs or _stale(OUT, objs):
         cmd = ["nvcc", "-shared", "-o", str(OUT)] + [str(o) for o in objs] + ["-gencode", "arch=compute_100a,code=sm_100a"]
         subprocess.check_call(cmd)
+    build_fastcall(force)
     return OUT
+
+
+FASTCALL = HERE / "gact" / "_fastcall.so"
+
+
+def build_fastcall(force: bool = False):
+    """The CPython entry points for the two hot calls (csrc/fastcall.c), linked against libgact_b200.so beside it.
+    Optional: without it the binding goes through ctypes.  Returns the path, or None when the compile failed."""
+    src = CSRC / "fastcall.c"
+    if not (force or _stale(FASTCALL, [src, OUT] + sorted(INCLUDE.glob("*.h")))):
+        return FASTCALL
+    import sysconfig
+    cmd = ["gcc", "-O2", "-shared", "-fPIC", f"-I{sysconfig.get_paths()['include']}", f"-I{INCLUDE}", str(src), "-o", str(FASTCALL),
+           f"-L{OUT.parent}", "-l:" + OUT.name, "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode:
+        print("fastcall module not built:", r.stderr.strip().splitlines()[-1] if r.stderr.strip() else r.returncode)
+        return None
+    return FASTCALL
 
 
 if __name__ == "__main__":

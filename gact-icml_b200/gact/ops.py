@@ -247,8 +247,8 @@ def quantize_compact(input, q_bit, seed):
     base = buf.data_ptr()
     guard, stream = nv.guard_and_stream(x)
     with guard:
-        st = nv.lib.gact_quantize(x.data_ptr(), code, n, q_bit, int(seed) & 0xFFFFFFFFFFFFFFFF, nv.RNG_CODE[config.rng_mode],
-                                  None, int(config.fma), base, base + off_min, base + off_scale, stream)
+        st = nv.quantize_call(x.data_ptr(), code, n, q_bit, int(seed) & 0xFFFFFFFFFFFFFFFF, nv.RNG_CODE[config.rng_mode],
+                              None, int(config.fma), base, base + off_min, base + off_scale, stream)
     global launch_count
     launch_count += 1
     if st:
@@ -265,7 +265,7 @@ def dequantize_compact(p, shape):
     base = p.buf.data_ptr()
     guard, stream = nv.guard_and_stream(out)
     with guard:
-        st = nv.lib.gact_dequantize(base, base + off_min, base + off_scale, code, p.n, p.bits, out.data_ptr(), stream)
+        st = nv.dequantize_call(base, base + off_min, base + off_scale, code, p.n, p.bits, out.data_ptr(), stream)
     global launch_count
     launch_count += 1
     if st:

@@ -114,3 +114,19 @@ def test_calc_precision_host_twin(golden_dir=None):
         calc_precision(torch.full((4,), 32, dtype=torch.int32), torch.ones(4), torch.full((4,), 256, dtype=torch.int64), 100.0)
     with pytest.raises(RuntimeError):
         calc_precision(torch.full((4,), 32, dtype=torch.int64), torch.ones(4), torch.full((4,), 256, dtype=torch.int64), 1e9)
+
+
+def test_fastcall_module_forwards_to_the_same_entry_points():
+    """gact/_fastcall.so (built by gact-icml_b200/build.py) must answer argument errors exactly as the ctypes route."""
+    from gact import _native as nv
+    assert nv._fastcall is not None, "gact/_fastcall.so was not built"
+    buf = ctypes.create_string_buffer(4096 + 64)
+    p = (ctypes.addressof(buf) + 63) & ~63
+    cases = [(p, 0, 512, 3, 0, 0, None, 1, p, p, p, None), (p, 9, 512, 2, 0, 0, None, 1, p, p, p, None),
+             (None, 0, 512, 2, 0, 0, None, 1, p, p, p, None), (p + 4, 0, 100, 2, 0, 0, None, 1, p, p, p, None),
+             (p, 0, -1, 2, 0, 0, None, 1, p, p, p, None), (p, 0, 512, 2, 2**64 - 1, 7, None, 1, p, p, p, None),
+             (p, 0, 0, 2, 0, 0, None, 1, p, p, p, None)]
+    for c in cases:
+        assert nv._fastcall.quantize(*c) == nv.lib.gact_quantize(*c)
+    for c in [(p, p, p, 0, 512, 3, p, None), (p, p, p, 7, 512, 2, p, None), (None, p, p, 0, 512, 2, p, None), (p, p, p, 0, 0, 2, p, None)]:
+        assert nv._fastcall.dequantize(*c) == nv.lib.gact_dequantize(*c)
