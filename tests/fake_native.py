@@ -84,6 +84,8 @@ class FakeNative:
     RNG_CODE = {"curand": 0, "fast": 1, "rtn": 2, "external": 3}
     GROUP = 256
     lib = FakeLib()
+    quantize_call = lib.gact_quantize
+    dequantize_call = lib.gact_dequantize
 
     @staticmethod
     def check(status, what):
