@@ -422,6 +422,7 @@ __global__ void __launch_bounds__(kPipeThreads, GACT_PIPE_MINB) quantize_pipe_ke
 
 // smallest number of whole chunks for which the ring kernel is used (see launch_quantize); gact_set_ring_min_chunks
 static std::atomic<int64_t> g_ring_min_chunks{1536};
+constexpr int kMaxDevices = 64;
 constexpr int64_t kSmallTileMaxGroups = 40960;      // 16-bit tensors of up to 20 MB take tiles of 4 groups
 
 // direct-load kernel over the tiles from a.tile_begin on (in tiles of TG groups)
@@ -457,7 +458,11 @@ static int launch_quantize(const QuantArgs& args, cudaStream_t s) {
     constexpr bool kUsePipe = (DT != GACT_F32) && (RNG != GACT_RNG_RTN);
     if constexpr (kUsePipe) {
         const int64_t nchunks = a.n / (kChunkBytes / Elem<DT>::kBytes);
-        static int pipe_ready = 0;          // 0 = not set up, 1 = usable, -1 = shared memory opt-in refused
+        // the shared-memory opt-in is a per-device attribute of the kernel: 0 = not set up, 1 = usable, -1 = refused
+        static int ready_on[kMaxDevices] = {0};
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = kMaxDevices - 1;
+        int& pipe_ready = ready_on[dev];
         if (pipe_ready == 0) {
             pipe_ready = cudaFuncSetAttribute(quantize_pipe_kernel<DT, BITS, RNG, FMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               kPipeStages * kChunkBytes) == cudaSuccess ? 1 : -1;
