@@ -369,7 +369,7 @@ def run_ours(args):
         }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(spec, sample_elems=1 << 24, reps=6)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
@@ -488,7 +488,7 @@ def run_reference(args):
     extra = reference_cuda_rows()
     if extra is not None:
         line["reference_cuda_kernels_on_this_gpu"] = extra
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -570,13 +570,36 @@ def run_training(args):
                 "compressed_tensors": len(bits), "bit_histogram": hist, "adapt_seconds": round(adapt_s, 2),
                 "peak_mem_GB": round(peak_mem / 2**30, 2), "final_loss": float(loss),
                 "gpu_launches": launches, "clocks": clocks}
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """Keep file descriptor 1 for the result line alone: libraries that write to stdout on their own (NCCL prints
+    its version there on the first collective) are sent to stderr for the rest of the run."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None, help="timed steps (default 200 for the sweep, 20 for training)")
