@@ -24,7 +24,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 SHIM = HERE / "ref_shim"
-DEFAULT_REF = Path(os.environ.get("GACT_REFERENCE_DIR", "/root/reference"))   # checkout of the reference
+# checkout of the reference: $GACT_REFERENCE_DIR, else a folder named "reference" beside this repository
+DEFAULT_REF = Path(os.environ.get("GACT_REFERENCE_DIR", str(HERE.parent.parent / "reference")))
 
 EXTENSIONS = {
     # name -> (sources relative to <ref>/gact/gact/cpp_extension, needs nvcc)
