@@ -1,9 +1,10 @@
 // 1-bit packing of dropout masks (uint8 or bool, one byte per element) and its inverse.
 //
 // Layout (kept from the reference so packed masks are interchangeable): element e of 512-element block
-// blk sits in bit (t / 16) of word blk*16 + (t % 16), t = e % 512.  Seen from a warp that owns one block
-// with lane k holding the 16 consecutive bytes t = 16k .. 16k+15, word w is exactly the ballot of "my byte
-// number w is non-zero": 16 ballots per block, no shared memory, no atomics.
+// blk sits in bit (t / 16) of word blk*16 + (t % 16), t = e % 512.  Seen from a warp that owns the block
+// with lane k holding the 16 consecutive bytes t = 16k .. 16k+15, the block is a 32 x 16 bit matrix (row k =
+// lane k's 16 "non-zero" bits) and its 16 words are the columns: a bit-matrix transpose across the warp, done
+// for two blocks at once (32 x 32) with five shuffle stages.  No shared memory, no atomics, no votes.
 // The packed mask has 16 words per started block, ceil(n/512)*16 in all: a partial last block still spreads
 // its elements over all 16 words.  (The reference allocates ceil(n/32) words and lets its last block store
 // and load past that allocation; for n a multiple of 512 the two sizes agree.)
@@ -13,65 +14,103 @@ namespace gact {
 
 constexpr int kMThreads = 256;
 
+// Transpose of a 32 x 32 bit matrix held one row per lane (bit j of lane i  ->  bit i of lane j): five butterfly
+// stages; in each, lanes whose index has bit s clear keep their low half-blocks and take the partner's low
+// half-blocks shifted up, the others keep their high half-blocks and take the partner's high ones shifted down.
+// Both shifts are one rotation (the bits that wrap around fall outside the selected mask).
+__device__ __forceinline__ uint32_t transpose_bits32(uint32_t x, int lane) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const uint32_t m = (s == 16) ? 0x0000FFFFu : (s == 8) ? 0x00FF00FFu : (s == 4) ? 0x0F0F0F0Fu : (s == 2) ? 0x33333333u : 0x55555555u;
+        const bool up = (lane & s) == 0;
+        const uint32_t y = __shfl_xor_sync(kFull, x, s);
+        const uint32_t t = __funnelshift_l(y, y, up ? s : 32 - s);
+        const uint32_t keep = up ? m : ~m;
+        x = (x & keep) | (t & ~keep);
+    }
+    return x;
+}
+
+// 16 bytes (four words) -> 16 bits, bit j set when byte j is non-zero
+__device__ __forceinline__ uint32_t nonzero_bits16(const uint32_t (&q)[4]) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        const uint32_t r = (((q[w] & 0x7f7f7f7fu) + 0x7f7f7f7fu) | q[w]) & 0x80808080u;   // bit 7 of every non-zero byte
+        m |= ((r * 0x00204081u) >> 28) << (4 * w);                                       // bits 7, 15, 23, 31 -> one nibble
+    }
+    return m;
+}
+
+// the 16 bytes of one lane in block blk (zero past the end of the tensor)
+__device__ __forceinline__ void load_mask16(const uint8_t* __restrict__ x, int64_t n, int64_t blk, int lane, uint32_t (&q)[4]) {
+    const int64_t base = blk * 512 + lane * 16;
+    if (blk * 512 + 512 <= n) {
+        const uint4 v = ld_stream_u4(x + base);
+        q[0] = v.x; q[1] = v.y; q[2] = v.z; q[3] = v.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            q[i] = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int64_t e = base + i * 4 + b;
+                if (e < n) q[i] |= (uint32_t)x[e] << (8 * b);
+            }
+        }
+    }
+}
+
+// A warp takes two 512-element blocks per step: lane k reads its 16 consecutive bytes of each, reduces them to
+// 16 + 16 bits, and one bit-matrix transpose across the warp turns the 32 rows into the 32 words of the two
+// blocks (lane j < 16: word j of the first block, lane 16 + j: word j of the second), written as one 128-byte row.
 __global__ void __launch_bounds__(kMThreads) mask_pack_kernel(const uint8_t* __restrict__ x, int64_t n, uint32_t* __restrict__ words,
                                                               int64_t nwords, int* not_binary) {
     const int lane = threadIdx.x & 31;
     const int64_t nblk = (n + 511) / 512;
+    const int64_t npair = (nblk + 1) / 2;
     const int64_t nwarps = (int64_t)gridDim.x * (kMThreads / 32);
-    bool odd = false;
-    for (int64_t blk = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); blk < nblk; blk += nwarps) {
-        const int64_t base = blk * 512 + lane * 16;
-        uint32_t q[4];
-        if (blk * 512 + 512 <= n) {
-            const uint4 v = ld_stream_u4(x + base);
-            q[0] = v.x; q[1] = v.y; q[2] = v.z; q[3] = v.w;
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                q[i] = 0;
-#pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    const int64_t e = base + i * 4 + b;
-                    if (e < n) q[i] |= (uint32_t)x[e] << (8 * b);
-                }
-            }
-        }
-        odd |= ((q[0] | q[1] | q[2] | q[3]) & 0xfefefefeu) != 0u;
-        uint32_t mine = 0;
-#pragma unroll
-        for (int w = 0; w < 16; w++) {
-            const uint32_t byte = (q[w >> 2] >> ((w & 3) * 8)) & 0xffu;
-            const uint32_t bal = __ballot_sync(kFull, byte != 0u);
-            if (lane == w) mine = bal;
-        }
-        const int64_t wi = blk * 16 + lane;
-        if (lane < 16 && wi < nwords) words[wi] = mine;
+    uint32_t seen = 0;
+    for (int64_t pair = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); pair < npair; pair += nwarps) {
+        uint32_t qa[4], qb[4] = {0, 0, 0, 0};
+        load_mask16(x, n, 2 * pair, lane, qa);
+        if (2 * pair + 1 < nblk) load_mask16(x, n, 2 * pair + 1, lane, qb);
+        seen |= qa[0] | qa[1] | qa[2] | qa[3] | qb[0] | qb[1] | qb[2] | qb[3];
+        const uint32_t row = nonzero_bits16(qa) | (nonzero_bits16(qb) << 16);
+        const uint32_t col = transpose_bits32(row, lane);
+        const int64_t wi = pair * 32 + lane;
+        if (wi < nwords) words[wi] = col;
     }
-    if (not_binary != nullptr && odd) *not_binary = 1;
+    if (not_binary != nullptr && (seen & 0xfefefefeu) != 0u) *not_binary = 1;
 }
 
 __global__ void __launch_bounds__(kMThreads) mask_unpack_kernel(const uint32_t* __restrict__ words, int64_t n, int64_t nwords,
                                                                 uint8_t* __restrict__ out) {
     const int lane = threadIdx.x & 31;
     const int64_t nblk = (n + 511) / 512;
+    const int64_t npair = (nblk + 1) / 2;
     const int64_t nwarps = (int64_t)gridDim.x * (kMThreads / 32);
-    for (int64_t blk = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); blk < nblk; blk += nwarps) {
-        const int64_t wi = blk * 16 + (lane & 15);
-        const uint32_t mine = (wi < nwords) ? words[wi] : 0u;
-        uint32_t q[4] = {0, 0, 0, 0};
+    for (int64_t pair = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); pair < npair; pair += nwarps) {
+        const int64_t wi = pair * 32 + lane;
+        const uint32_t col = (wi < nwords) ? words[wi] : 0u;
+        const uint32_t row = transpose_bits32(col, lane);      // low half: my 16 elements of the first block, high half: second block
 #pragma unroll
-        for (int w = 0; w < 16; w++) {
-            const uint32_t word = __shfl_sync(kFull, mine, w);
-            q[w >> 2] |= ((word >> lane) & 1u) << ((w & 3) * 8);
-        }
-        const int64_t base = blk * 512 + lane * 16;
-        if (blk * 512 + 512 <= n) {
-            st_stream_u4(out + base, make_uint4(q[0], q[1], q[2], q[3]));
-        } else {
+        for (int h = 0; h < 2; h++) {
+            const int64_t blk = 2 * pair + h;
+            if (blk >= nblk) break;
+            const uint32_t m = (row >> (16 * h)) & 0xffffu;
+            uint32_t q[4];
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int64_t e = base + i;
-                if (e < n) out[e] = (uint8_t)((q[i >> 2] >> ((i & 3) * 8)) & 0xffu);
+            for (int w = 0; w < 4; w++) q[w] = (((m >> (4 * w)) & 0xfu) * 0x00204081u) & 0x01010101u;   // bit i -> byte i
+            const int64_t base = blk * 512 + lane * 16;
+            if (blk * 512 + 512 <= n) {
+                st_stream_u4(out + base, make_uint4(q[0], q[1], q[2], q[3]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const int64_t e = base + i;
+                    if (e < n) out[e] = (uint8_t)((q[i >> 2] >> ((i & 3) * 8)) & 0xffu);
+                }
             }
         }
     }
@@ -82,8 +121,8 @@ __global__ void __launch_bounds__(kMThreads) mask_unpack_kernel(const uint32_t* 
 using namespace gact;
 
 static int mask_blocks(int64_t n) {
-    const int64_t nblk = (n + 511) / 512;
-    const int64_t want = (nblk + kMThreads / 32 - 1) / (kMThreads / 32);
+    const int64_t npair = ((n + 511) / 512 + 1) / 2;              // a warp step covers two 512-element blocks
+    const int64_t want = (npair + kMThreads / 32 - 1) / (kMThreads / 32);
     const int64_t cap = (int64_t)kSMs * 8;
     return (int)(want < cap ? want : cap);
 }
