@@ -376,6 +376,15 @@ def run_ours(args):
 
 
 # ----------------------------------------------------------------------------------------------------------------
+def use_all_host_threads(oracle):
+    """The CPU arm runs on every core this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    oracle.set_threads(max(1, cores))
+
+
 def cpu_sample(spec, sample_elems):
     """Bounded sample of the workload for the CPU runs: the first `sample_elems` elements of the eight big cases
     and of the first eight mixed tensors (same dtypes, widths and distributions)."""
@@ -402,6 +411,7 @@ def cpu_pass(cases, seed):
 
 def cpu_baseline(spec, sample_elems, reps):
     import oracle
+    use_all_host_threads(oracle)
     cases = cpu_sample(spec, sample_elems)
     cpu_pass(cases[:2], 0)
     by, dt = 0, 0.0
@@ -467,6 +477,7 @@ def run_reference(args):
     if rank != 0:
         return
     import oracle
+    use_all_host_threads(oracle)
     spec = workload_spec()
     sample = 1 << 22
     cases = cpu_sample(spec, sample)
