@@ -1,7 +1,7 @@
 // Fused quantize: per-group min/max -> scale -> stochastic rounding -> bit packing, one pass over the input.
 //
-// Work decomposition.  A warp owns a tile of GPW consecutive groups (8 for the 16-bit types, max(4, wpt) for
-// fp32), i.e. U = GPW/wpt whole row-blocks of the packed layout.  Each lane keeps its 8 consecutive values of
+// Work decomposition.  A warp owns a tile of GPW consecutive groups (8 for the 16-bit types - 4 for small
+// tensors -, max(4, wpt) for fp32), i.e. U = GPW/wpt whole row-blocks of the packed layout.  Each lane keeps its 8 consecutive values of
 // every group of the tile in registers, in storage format; all loads of a tile are issued before anything is
 // reduced (4-8 KB in flight per warp).  min/max: two-wide min/max on the packed pairs inside the lane, then one
 // warp-reduction instruction each (redux.sync.min/max.f32).  Lane k works out the scale of group k (the
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(kQThreads, GACT_QMINB) quantize_kernel(const _
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Bulk-copy pipeline (the main path).  Persistent CTAs of 8 consumer warps + 1 producer warp.  The producer's
+// Bulk-copy pipeline (large 16-bit tensors with generated noise, see launch_quantize).  Persistent CTAs of 8 consumer warps + 1 producer warp.  The producer's
 // elected lane streams chunks of the input (one tile per consumer warp: 32 KB, or 64 KB for 1-bit fp32) into a
 // 3-stage (2 for the 64 KB chunks) shared-memory ring with cp.async.bulk (the TMA
 // engine, plain 1-D copies of this GPU's own memory, no multicast); an mbarrier per stage counts the bytes in.
