@@ -71,15 +71,29 @@ __global__ void __launch_bounds__(kMThreads) mask_pack_kernel(const uint8_t* __r
     const int64_t npair = (nblk + 1) / 2;
     const int64_t nwarps = (int64_t)gridDim.x * (kMThreads / 32);
     uint32_t seen = 0;
-    for (int64_t pair = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); pair < npair; pair += nwarps) {
-        uint32_t qa[4], qb[4] = {0, 0, 0, 0};
-        load_mask16(x, n, 2 * pair, lane, qa);
-        if (2 * pair + 1 < nblk) load_mask16(x, n, 2 * pair + 1, lane, qb);
-        seen |= qa[0] | qa[1] | qa[2] | qa[3] | qb[0] | qb[1] | qb[2] | qb[3];
-        const uint32_t row = nonzero_bits16(qa) | (nonzero_bits16(qb) << 16);
-        const uint32_t col = transpose_bits32(row, lane);
-        const int64_t wi = pair * 32 + lane;
-        if (wi < nwords) words[wi] = col;
+    // two pairs (four blocks, 64 bytes per lane) per step, all loads first
+    const int64_t nstep = (npair + 1) / 2;
+    for (int64_t step = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); step < nstep; step += nwarps) {
+        uint32_t q[4][4];
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int64_t blk = 4 * step + b;
+            if (blk < nblk) {
+                load_mask16(x, n, blk, lane, q[b]);
+            } else {
+                q[b][0] = q[b][1] = q[b][2] = q[b][3] = 0;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t (&qa)[4] = q[2 * h];
+            const uint32_t (&qb)[4] = q[2 * h + 1];
+            seen |= qa[0] | qa[1] | qa[2] | qa[3] | qb[0] | qb[1] | qb[2] | qb[3];
+            const uint32_t row = nonzero_bits16(qa) | (nonzero_bits16(qb) << 16);
+            const uint32_t col = transpose_bits32(row, lane);
+            const int64_t wi = (2 * step + h) * 32 + lane;
+            if (wi < nwords) words[wi] = col;
+        }
     }
     if (not_binary != nullptr && (seen & 0xfefefefeu) != 0u) *not_binary = 1;
 }
@@ -120,9 +134,9 @@ __global__ void __launch_bounds__(kMThreads) mask_unpack_kernel(const uint32_t* 
 
 using namespace gact;
 
-static int mask_blocks(int64_t n) {
-    const int64_t npair = ((n + 511) / 512 + 1) / 2;              // a warp step covers two 512-element blocks
-    const int64_t want = (npair + kMThreads / 32 - 1) / (kMThreads / 32);
+static int mask_blocks(int64_t n, int blocks_per_step) {
+    const int64_t nstep = ((n + 511) / 512 + blocks_per_step - 1) / blocks_per_step;   // warp steps in all
+    const int64_t want = (nstep + kMThreads / 32 - 1) / (kMThreads / 32);
     const int64_t cap = (int64_t)kSMs * 8;
     return (int)(want < cap ? want : cap);
 }
@@ -134,7 +148,7 @@ extern "C" int gact_mask_pack(const uint8_t* x, int64_t n, uint32_t* words, int*
     if (n == 0) return GACT_OK;
     if (!x || !words) return GACT_ERR_NULL;
     if (((uintptr_t)x & 15) || ((uintptr_t)words & 3)) return GACT_ERR_ALIGN;
-    mask_pack_kernel<<<mask_blocks(n), kMThreads, 0, (cudaStream_t)stream>>>(x, n, words, (n + 511) / 512 * 16, not_binary);
+    mask_pack_kernel<<<mask_blocks(n, 4), kMThreads, 0, (cudaStream_t)stream>>>(x, n, words, (n + 511) / 512 * 16, not_binary);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }
 
@@ -143,6 +157,6 @@ extern "C" int gact_mask_unpack(const uint32_t* words, int64_t n, uint8_t* out, 
     if (n == 0) return GACT_OK;
     if (!words || !out) return GACT_ERR_NULL;
     if (((uintptr_t)out & 15) || ((uintptr_t)words & 3)) return GACT_ERR_ALIGN;
-    mask_unpack_kernel<<<mask_blocks(n), kMThreads, 0, (cudaStream_t)stream>>>(words, n, (n + 511) / 512 * 16, out);
+    mask_unpack_kernel<<<mask_blocks(n, 2), kMThreads, 0, (cudaStream_t)stream>>>(words, n, (n + 511) / 512 * 16, out);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }
