@@ -104,26 +104,35 @@ __global__ void __launch_bounds__(kMThreads) mask_unpack_kernel(const uint32_t* 
     const int64_t nblk = (n + 511) / 512;
     const int64_t npair = (nblk + 1) / 2;
     const int64_t nwarps = (int64_t)gridDim.x * (kMThreads / 32);
-    for (int64_t pair = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); pair < npair; pair += nwarps) {
-        const int64_t wi = pair * 32 + lane;
-        const uint32_t col = (wi < nwords) ? words[wi] : 0u;
-        const uint32_t row = transpose_bits32(col, lane);      // low half: my 16 elements of the first block, high half: second block
+    // two pairs (four blocks) per step: both word loads first, then 64 bytes of stores per lane
+    const int64_t nstep = (npair + 1) / 2;
+    for (int64_t step = (int64_t)blockIdx.x * (kMThreads / 32) + (threadIdx.x >> 5); step < nstep; step += nwarps) {
+        uint32_t col[2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int64_t blk = 2 * pair + h;
-            if (blk >= nblk) break;
-            const uint32_t m = (row >> (16 * h)) & 0xffffu;
-            uint32_t q[4];
+            const int64_t wi = (2 * step + h) * 32 + lane;
+            col[h] = (wi < nwords) ? words[wi] : 0u;
+        }
 #pragma unroll
-            for (int w = 0; w < 4; w++) q[w] = (((m >> (4 * w)) & 0xfu) * 0x00204081u) & 0x01010101u;   // bit i -> byte i
-            const int64_t base = blk * 512 + lane * 16;
-            if (blk * 512 + 512 <= n) {
-                st_stream_u4(out + base, make_uint4(q[0], q[1], q[2], q[3]));
-            } else {
+        for (int h = 0; h < 2; h++) {
+            const uint32_t row = transpose_bits32(col[h], lane);   // low half: my 16 elements of the pair's first block, high half: second
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int64_t e = base + i;
-                    if (e < n) out[e] = (uint8_t)((q[i >> 2] >> ((i & 3) * 8)) & 0xffu);
+            for (int k = 0; k < 2; k++) {
+                const int64_t blk = 4 * step + 2 * h + k;
+                if (blk >= nblk) break;
+                const uint32_t m = (row >> (16 * k)) & 0xffffu;
+                uint32_t q[4];
+#pragma unroll
+                for (int w = 0; w < 4; w++) q[w] = (((m >> (4 * w)) & 0xfu) * 0x00204081u) & 0x01010101u;   // bit i -> byte i
+                const int64_t base = blk * 512 + lane * 16;
+                if (blk * 512 + 512 <= n) {
+                    st_stream_u4(out + base, make_uint4(q[0], q[1], q[2], q[3]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int64_t e = base + i;
+                        if (e < n) out[e] = (uint8_t)((q[i >> 2] >> ((i & 3) * 8)) & 0xffu);
+                    }
                 }
             }
         }
@@ -157,6 +166,6 @@ extern "C" int gact_mask_unpack(const uint32_t* words, int64_t n, uint8_t* out, 
     if (n == 0) return GACT_OK;
     if (!words || !out) return GACT_ERR_NULL;
     if (((uintptr_t)out & 15) || ((uintptr_t)words & 3)) return GACT_ERR_ALIGN;
-    mask_unpack_kernel<<<mask_blocks(n, 2), kMThreads, 0, (cudaStream_t)stream>>>(words, n, (n + 511) / 512 * 16, out);
+    mask_unpack_kernel<<<mask_blocks(n, 4), kMThreads, 0, (cudaStream_t)stream>>>(words, n, (n + 511) / 512 * 16, out);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }
