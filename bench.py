@@ -1,20 +1,27 @@
 #!/usr/bin/env python
-"""Benchmark of the activation-compression hot path (quantize + dequantize GB/s).
+"""Benchmark of the activation-compression hot path (quantize + dequantize GB/s) and of compressed training.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--rng curand|fast|rtn]
-    python bench.py --workload bert_large|resnet50|gcn [--level L2] [--batch B]      (training samples/s)
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--rng curand|fast|rtn] [--no-train]
+    python bench.py --impl reference [--gpus N] [--steps K] [--warmup W]
+    python bench.py --workload bert_large|resnet50|gcn [--level L2] [--batch B] [--get-mem] [--impl reference]
+    python bench.py --case f16:2:fast --numel 102760448 --reps 3 [--relu]        (one kernel case, for profilers)
+    python bench.py --case mask --numel 411041792 --reps 3
 
-Workload (the kernel sweep the metric is quoted on): post-ReLU activations of shape
-128x64x112x112 in fp16 and bf16 at 1/2/4/8 bits, plus a mixed list of 50 fp16 tensors of 2^20..2^26 elements with
-widths drawn from {2,4,8}.  One step = a "forward" phase that quantizes every tensor of the set followed by a
-"backward" phase that dequantizes them in reverse order, so that nothing a kernel reads is still in L2 from the
-kernel that wrote it (the set moves ~10 GB per step; every big tensor is larger than L2).
-`value` = algorithmic bytes (tensor + packed codes + per-group min and scale, each counted once) of all launches of all ranks / max-over-ranks device
-time, inputs resident in HBM.  `e2e` = the same bytes through the public ops (gact.ops.op_quantize /
-op_dequantize) starting from pinned host buffers and ending with the reconstructed tensors back in host memory.
+Default workload (the kernel sweep the metric is quoted on): post-ReLU activations of shape 128x64x112x112 in fp16 and
+bf16 at 1/2/4/8 bits, plus a mixed list of 50 fp16 tensors of 2^20..2^26 elements with widths drawn from {2,4,8}.  One
+pass = a "forward" phase that quantizes every tensor of the set followed by a "backward" phase that dequantizes them
+in reverse order, so that nothing a kernel reads is still in L2 from the kernel that wrote it (the set moves ~10 GB
+per pass; every big tensor is larger than L2).  One step = `passes_per_step` passes, chosen so that the timed
+region lasts about a second.  `value` = algorithmic bytes (tensor + packed codes + per-group min and scale, each
+counted once) of all launches of all ranks / max-over-ranks device time, inputs resident in HBM.  `e2e` = the same
+bytes through the public ops (gact.ops.op_quantize / op_dequantize) starting from pinned host buffers and ending with
+the reconstructed tensors back in host memory.  `train` = BERT-large sequence-classification training (batch 64 per
+GPU, seq 128, bf16 autocast, AdamW; DDP over NCCL for N > 1) without compression (L0) and with auto-precision
+compression (L2): samples/s over the steps after the adaptation step.
 
 `--impl reference` times the CPU restatement of the reference quantizer (the oracle; the reference has no CPU
-implementation of its own) on the host cores over a bounded sample of the same workload.
+implementation of its own) on the host cores over a bounded sample of the same workload; with `--workload` it runs
+the reference's own Python package on its own CUDA extensions (built unmodified into oracle/_ref) instead.
 
 One process per GPU under torchrun for N > 1: every rank compresses its own tensors, no collective on the data
 path (weak scaling).  Rank 0 prints exactly one JSON line on stdout.
@@ -22,8 +29,11 @@ path (weak scaling).  Rank 0 prints exactly one JSON line on stdout.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
+import math
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -39,10 +49,11 @@ import torch  # noqa: E402
 
 GROUP = 256
 METRIC = "act quant+dequant GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one quantize_pipe_kernel launch on the relu fp16 2-bit case (ncu,
-# profiles/quantize_pipe_kernel_f16_b2_relu_128x64x112x112.md)
+# DRAM read + write of one quantize16 launch on the relu fp16 2-bit tensor (ncu dram__bytes_read.sum +
+# dram__bytes_write.sum; the input is read once, part of the output is still in L2 when the kernel ends)
 DOM_TRAFFIC_BYTES = 218672384
 BIG_SHAPE = (128, 64, 112, 112)
+DTYPES = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 
 
 def alg_bytes(n: int, bits: int, elem_size: int, scale_size: int) -> int:
@@ -57,9 +68,7 @@ def workload_spec():
     """[(name, dtype, numel, bits)] of the sweep.  Mixed list: numel = 2^k, k ~ U{20..26} (seed 1), bits ~ U{2,4,8}
     (seed 2)."""
     spec = []
-    n_big = 1
-    for s in BIG_SHAPE:
-        n_big *= s
+    n_big = math.prod(BIG_SHAPE)
     for dt in (torch.float16, torch.bfloat16):
         for bits in (1, 2, 4, 8):
             spec.append((f"relu_{str(dt).split('.')[-1]}_b{bits}", dt, n_big, bits))
@@ -184,12 +193,12 @@ def run_ours(args):
     DOM = 1                                   # the launch the roofline is quoted on: relu fp16, 2 bit
     dom_events = []
 
-    def forward_phase(step, timed=False):
+    def forward_phase(seed, timed=False):
         for i, ((name, dt, n, bits), x) in enumerate(zip(spec, xs)):
             pk, mn, sc = bufs[i]
             if timed and i == DOM:
                 e0 = torch.cuda.Event(enable_timing=True); e0.record(stream)
-            st = nv.lib.gact_quantize(x.data_ptr(), nv.DTYPE_CODE[dt], n, bits, i + step, mode, None, 1, pk.data_ptr(),
+            st = nv.lib.gact_quantize(x.data_ptr(), nv.DTYPE_CODE[dt], n, bits, i + seed, mode, None, 1, pk.data_ptr(),
                                       mn.data_ptr(), sc.data_ptr(), sp)
             if timed and i == DOM:
                 e1 = torch.cuda.Event(enable_timing=True); e1.record(stream)
@@ -211,24 +220,38 @@ def run_ours(args):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    # warm-up passes, the last of them timed to size the steps: one step = R passes, R such that the K timed steps
+    # last about a second (the same R on every rank)
     for w in range(args.warmup):
         forward_phase(w); backward_phase()
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record(stream); forward_phase(args.warmup); backward_phase(); c1.record(stream)
+    torch.cuda.synchronize()
+    est = torch.tensor([c0.elapsed_time(c1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(est, op=torch.distributed.ReduceOp.MAX)
+    R = args.passes if args.passes > 0 else max(1, min(64, int(math.ceil(args.min_region_ms / (args.steps * float(est.item()))))))
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps * R + 1)]
     ev[0].record(stream)
+    j = 0
     for k in range(args.steps):
-        forward_phase(args.warmup + k, timed=True)
-        ev[2 * k + 1].record(stream)
-        backward_phase()
-        ev[2 * k + 2].record(stream)
+        for r in range(R):
+            forward_phase(args.warmup + 1 + k * R + r, timed=(r == 0))
+            ev[2 * j + 1].record(stream)
+            backward_phase()
+            ev[2 * j + 2].record(stream)
+            j += 1
     barrier()
     total_ms = ev[0].elapsed_time(ev[-1])
-    q_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps))
-    d_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(args.steps))
+    q_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps * R))
+    d_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(args.steps * R))
     clocks = sampler.stop() if rank == 0 else None
+    passes = args.steps * R
 
     # ---- per-kernel table on rank 0 (stderr): every case timed alone with an L2 flush between launches ------
     table = {}
@@ -330,9 +353,26 @@ def run_ours(args):
     if world > 1:
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
     total_ms, q_ms, d_ms, e2e_ms = times.tolist()
-    step_bytes = spec_bytes(spec)
-    value = world * step_bytes * args.steps / (total_ms * 1e-3) / 1e9
-    e2e_value = world * step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    pass_bytes = spec_bytes(spec)
+    value = world * pass_bytes * passes / (total_ms * 1e-3) / 1e9
+    e2e_value = world * pass_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    dom_us = sum(a.elapsed_time(b) for a, b in dom_events) / max(len(dom_events), 1) * 1e3
+    n_dom = len(dom_events)
+
+    # ---- training: BERT-large data parallel, L0 and L2 ----------------------------------------------------------
+    del bufs, out_big, xs, host_in, host_out, e2e_done, dom_events
+    gc.collect()
+    torch.cuda.empty_cache()
+    train = None
+    if not args.no_train:
+        train = {}
+        for level in ("L0", "L2"):
+            res = train_once(args, "bert_large", level, dev, rank, world, steps=args.train_steps, warmup=3)
+            if rank == 0:
+                train[level] = res
+        if rank == 0:
+            train["L2_over_L0"] = round(train["L2"]["samples_per_s"] / train["L0"]["samples_per_s"], 3)
+            train["workload"] = "BERT-large seq-cls, seq 128, batch 64 per GPU, AdamW, bf16 autocast, synthetic tokens; DDP over NCCL for N > 1"
 
     if rank == 0:
         peaks = {}
@@ -341,10 +381,9 @@ def run_ours(args):
             peaks = json.loads(pk_path.read_text())
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-        q_gbps = (step_bytes / 2) * args.steps / (q_ms * 1e-3) / 1e9
-        d_gbps = (step_bytes / 2) * args.steps / (d_ms * 1e-3) / 1e9
+        q_gbps = (pass_bytes / 2) * passes / (q_ms * 1e-3) / 1e9
+        d_gbps = (pass_bytes / 2) * passes / (d_ms * 1e-3) / 1e9
         n_launch = len(spec)
-        dom_us = sum(a.elapsed_time(b) for a, b in dom_events) / max(len(dom_events), 1) * 1e3
         dom_bytes = alg_bytes(spec[DOM][2], spec[DOM][3], 2, 2)
         dom_gbps = dom_bytes / (dom_us * 1e-6) / 1e9 if dom_us > 0 else 0.0
         line = {
@@ -352,10 +391,10 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16/bf16 in, u8 codes", "data": "synthetic",
             "config": {"workload": "kernel sweep: relu 128x64x112x112 fp16+bf16 x bits{1,2,4,8} + 50 mixed fp16 tensors 2^20..2^26 x bits{2,4,8}",
-                       "group_size": GROUP, "rng": args.rng, "l2": "inputs larger than L2; all quantizes of a step run before its dequantizes",
-                       "bytes_per_step_per_gpu": step_bytes},
+                       "group_size": GROUP, "rng": args.rng, "l2": "inputs larger than L2; all quantizes of a pass run before its dequantizes",
+                       "passes_per_step": R, "bytes_per_pass_per_gpu": pass_bytes, "bytes_per_step_per_gpu": pass_bytes * R},
             "pct_of_8TBps": round(100 * value / world / 8000.0, 1),
-            "roofline": {"kernel": "quantize_pipe_kernel<f16, 2 bit, %s> on relu 128x64x112x112 (%d launches timed inside the steps)" % (args.rng, len(dom_events)),
+            "roofline": {"kernel": "quantize16_kernel<f16, 2 bit, %s> on relu 128x64x112x112 (%d launches timed inside the steps)" % (args.rng, n_dom),
                          "bound": "hbm", "achieved": round(dom_gbps, 1), "peak": peak, "unit": "GB/s", "frac": round(dom_gbps / peak, 3),
                          "traffic": DOM_TRAFFIC_BYTES, "algorithmic_bytes": dom_bytes, "avg_launch_us": round(dom_us, 2),
                          "peak_source": peak_src,
@@ -363,10 +402,12 @@ def run_ours(args):
                          "all_dequantize_launches": {"achieved": round(d_gbps, 1), "frac": round(d_gbps / peak, 3)}},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "api": "gact.ops.op_quantize/op_dequantize from pinned host buffers; copy-in, compute and copy-out on three streams"},
-            "gpu_launches": 2 * n_launch * args.steps,
+            "gpu_launches": 2 * n_launch * passes,
             "clocks": clocks,
             "kernels": table,
         }
+        if train is not None:
+            line["train"] = train
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(spec, sample_elems=1 << 24, reps=6)
         emit(line)
@@ -376,13 +417,12 @@ def run_ours(args):
 
 
 # ----------------------------------------------------------------------------------------------------------------
-def use_all_host_threads(oracle):
-    """The CPU arm runs on every core this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)."""
+def host_threads():
+    """Host threads this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)."""
     try:
-        cores = len(os.sched_getaffinity(0))
+        return len(os.sched_getaffinity(0))
     except AttributeError:
-        cores = os.cpu_count() or 1
-    oracle.set_threads(max(1, cores))
+        return os.cpu_count() or 1
 
 
 def cpu_sample(spec, sample_elems):
@@ -411,7 +451,7 @@ def cpu_pass(cases, seed):
 
 def cpu_baseline(spec, sample_elems, reps):
     import oracle
-    use_all_host_threads(oracle)
+    oracle.set_threads(host_threads())
     cases = cpu_sample(spec, sample_elems)
     cpu_pass(cases[:2], 0)
     by, dt = 0, 0.0
@@ -437,9 +477,7 @@ def reference_cuda_rows():
     if q is None or m is None:
         return None
     dev = torch.device("cuda", 0)
-    n = 1
-    for s_ in BIG_SHAPE:
-        n *= s_
+    n = math.prod(BIG_SHAPE)
     G = n // GROUP
     x = torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(1234)).clamp_min_(0).half()
     groups = x.view(G, GROUP)
@@ -472,119 +510,278 @@ def reference_cuda_rows():
 
 def run_reference(args):
     """The reference has no CPU implementation of this path (every entry point demands CUDA tensors), so its
-    arm is the CPU restatement of its kernels (the oracle), on all host threads, over a bounded sample."""
+    arm is the CPU restatement of its kernels (the oracle) over a bounded sample.  Under torchrun every rank runs
+    the sample on its share of the host cores and the bytes are summed over the ranks, as the GPU arm sums its
+    ranks' bytes."""
     rank, world, local = dist_env()
-    if rank != 0:
-        return
     import oracle
-    use_all_host_threads(oracle)
+    threads = max(1, host_threads() // world)
+    oracle.set_threads(threads)
+    if world > 1:
+        torch.distributed.init_process_group("gloo")
     spec = workload_spec()
     sample = 1 << 22
     cases = cpu_sample(spec, sample)
     for w in range(args.warmup):
         cpu_pass(cases[:4], w)
+    if world > 1:
+        torch.distributed.barrier()
     by, dt = 0, 0.0
     for k in range(args.steps):
         b, t = cpu_pass(cases, k)
         by += b; dt += t
-    v = round(by / dt / 1e9, 3)
-    base = {"value": v, "unit": "GB/s", "cores": oracle.threads(), "kind": "port",
-            "sample": f"per step: first {sample} elements of the 8 big cases and of 8 mixed tensors, quantize+dequantize"}
-    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16/bf16 in, u8 codes", "data": "synthetic",
-            "config": {"workload": "kernel sweep (bounded sample on host cores)", "group_size": GROUP, "rng": "curand"},
-            "cpu_baseline": base,
-            "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    extra = reference_cuda_rows()
-    if extra is not None:
-        line["reference_cuda_kernels_on_this_gpu"] = extra
-    emit(line)
+    red = torch.tensor([float(by), dt, float(oracle.threads())], dtype=torch.float64)
+    if world > 1:
+        mx = red.clone()
+        torch.distributed.all_reduce(red, op=torch.distributed.ReduceOp.SUM)
+        torch.distributed.all_reduce(mx, op=torch.distributed.ReduceOp.MAX)
+        by, dt, cores = red[0].item(), mx[1].item(), int(red[2].item())
+    else:
+        cores = int(red[2].item())
+    if rank == 0:
+        v = round(by / dt / 1e9, 3)
+        base = {"value": v, "unit": "GB/s", "cores": cores, "kind": "port",
+                "sample": f"per step and rank: first {sample} elements of the 8 big cases and of 8 mixed tensors, quantize+dequantize; "
+                          f"{world} rank(s) x {threads} thread(s)"}
+        line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16/bf16 in, u8 codes", "data": "synthetic",
+                "config": {"workload": "kernel sweep (bounded sample on host cores)", "group_size": GROUP, "rng": "curand"},
+                "cpu_baseline": base,
+                "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        extra = reference_cuda_rows()
+        if extra is not None:
+            line["reference_cuda_kernels_on_this_gpu"] = extra
+        emit(line)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
 
 
 # ----------------------------------------------------------------------------------------------------------------
-def run_training(args):
-    """End-to-end training throughput (samples/s) of a synthetic-data workload with saved-tensor compression."""
-    import statistics
-
+def import_gact(reference: bool):
+    """The product's `gact`, or - for the reference training arm - the reference's own Python package on its own CUDA
+    extensions, as oracle/build_ref.py installed them (unmodified) under oracle/_ref/pkg.  Returns the module, or None
+    when the reference package is not there."""
+    if reference:
+        pkg = ROOT / "oracle" / "_ref" / "pkg"
+        if not (pkg / "gact" / "__init__.py").exists():
+            return None
+        sys.path.insert(0, str(pkg))
     import gact
-    import gact.ops
-    import workloads
+    return gact
 
-    rank, world, local = dist_env()
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=dev)
-    gact.config.reset()
-    gact.set_optimization_level(args.level)
-    gact.config.rng_mode = args.rng
-    gact.config.dp_probe = args.dp_probe
+
+AUTOCAST = {"bf16": torch.bfloat16, "fp16": torch.float16, "off": None}
+
+
+def train_once(args, workload, level, dev, rank, world, steps, warmup, reference=False, get_mem=False):
+    """Builds the workload, runs the adaptation step, `warmup` steps and `steps` timed steps (CUDA events, barrier and
+    synchronize on both sides, max over ranks), and tears everything down again.  The loop is the reference
+    drivers': step, then controller.iterate(backprop) (benchmark/text_classification/run_glue.py:577-623,
+    benchmark/vision/train.py:316-350).  Returns the result dict on every rank."""
+    import workloads
+    gact = import_gact(reference)
+    if hasattr(gact.config, "reset"):
+        gact.config.reset()
+    else:                                      # the reference keeps whatever an earlier level left behind
+        gact.config.swap = gact.config.prefetch = False
+    gact.set_optimization_level(level)
+    if not reference:
+        gact.config.rng_mode = args.rng
+        gact.config.dp_probe = args.dp_probe
     workloads.DDP_BUCKET_MB = args.bucket_mb
     kw = {"world": world, "seed": rank}
     if args.batch:
         kw["batch"] = args.batch
-    if args.workload == "bert_large" and args.layers:
+    if workload == "bert_large" and args.layers:
         kw["layers"] = args.layers
-    wl = workloads.BUILDERS[args.workload](dev, **kw)
-    ctl = gact.Controller(wl.model)
+    if workload != "gcn" and args.autocast is not None:
+        kw["autocast"] = AUTOCAST[args.autocast]
+    wl = workloads.BUILDERS[workload](dev, **kw)
+    from gact.controller import Controller
+    ctl = Controller(wl.model)
     ctl.install_hook()
+    launch_counter = None if reference else sys.modules["gact.ops"].launches
 
     def barrier():
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    t_adapt0 = time.perf_counter()
-    loss = wl.step()
-    ctl.iterate(wl.backprop)                       # first iteration: the sensitivity probe + bit allocation
-    barrier()
-    adapt_s = time.perf_counter() - t_adapt0
-    for _ in range(max(args.warmup - 1, 0)):
+    def one_step():
         loss = wl.step()
         ctl.iterate(wl.backprop)
-    barrier()
-    torch.cuda.reset_peak_memory_stats()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = gact.ops.launch_count
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    ev[0].record()
-    for k in range(args.steps):
-        loss = wl.step()
-        ctl.iterate(wl.backprop)
-        ev[k + 1].record()
-    barrier()
-    total_ms = ev[0].elapsed_time(ev[-1])
-    per_step = [ev[k].elapsed_time(ev[k + 1]) for k in range(args.steps)]
-    clocks = sampler.stop() if rank == 0 else None
-    launches = gact.ops.launch_count - launches0
-    peak_mem = torch.cuda.max_memory_allocated()
-    ctl.uninstall_hook()
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        return loss
+
+    try:
+        t_adapt0 = time.perf_counter()
+        loss = one_step()                          # first iteration: the sensitivity probe + bit allocation
+        barrier()
+        adapt_s = time.perf_counter() - t_adapt0
+        for _ in range(max(warmup - 1, 0)):
+            loss = one_step()
+        barrier()
+        torch.cuda.reset_peak_memory_stats()
+        sampler = ClockSampler(dev.index)
+        if rank == 0:
+            sampler.start()
+        launches0 = launch_counter() if launch_counter else 0
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record()
+        for k in range(steps):
+            loss = one_step()
+            ev[k + 1].record()
+        barrier()
+        total_ms = ev[0].elapsed_time(ev[-1])
+        per_step = [ev[k].elapsed_time(ev[k + 1]) for k in range(steps)]
+        clocks = sampler.stop() if rank == 0 else None
+        launches = (launch_counter() - launches0) if launch_counter else None
+        peak_mem = torch.cuda.max_memory_allocated()
+        mem = workloads.activation_memory(wl, lambda: ctl.iterate(wl.backprop)) if get_mem or args.train_mem else None
+        final_loss = float(loss)
+    finally:
+        ctl.uninstall_hook()
+    t = torch.tensor([total_ms, statistics.median(per_step)], dtype=torch.float64, device=dev)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    total_ms = float(t.item())
+    total_ms, med_ms = t.tolist()
+    compress = getattr(gact.config, "compress_activation", False)
+    bits = dict(ctl.quantizer.bits) if compress else {}
+    hist = {}
+    for b in bits.values():
+        hist[str(b)] = hist.get(str(b), 0) + 1
+    res = {"samples_per_s": round(world * wl.samples_per_step * steps / (total_ms * 1e-3), 2),
+           "samples_per_s_median_step": round(world * wl.samples_per_step / (med_ms * 1e-3), 2),
+           "ms_per_step": round(total_ms / steps, 3), "median_ms_per_step": round(med_ms, 3), "steps": steps,
+           "adapt_seconds": round(adapt_s, 2), "compressed_tensors": len(bits), "bit_histogram": hist,
+           "peak_mem_GB": round(peak_mem / 2**30, 2), "final_loss": final_loss, "gpu_launches": launches, "clocks": clocks,
+           "describe": wl.describe, "name": wl.name}
+    if mem is not None:
+        res["memory"] = mem
+    del wl, ctl
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_training(args):
+    """`--workload X`: training throughput (samples/s) of one synthetic-data workload at one level; with `--get-mem`
+    also the activation memory of a step and a batch ladder; with `--impl reference` on the reference's own code."""
+    rank, world, local = dist_env()
+    reference = args.impl == "reference"
+    if reference and import_gact(True) is None:
+        if rank == 0:
+            emit({"impl": "reference", "unavailable": "oracle/_ref/pkg (the reference package installed by oracle/build_ref.py) is missing"})
+        return
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    res = train_once(args, args.workload, args.level, dev, rank, world, steps=args.steps, warmup=args.warmup,
+                     reference=reference, get_mem=args.get_mem)
+    ladder = None
+    if args.get_mem and world == 1 and args.workload != "gcn":
+        ladder = memory_ladder(args, dev, reference)
     if rank == 0:
-        value = world * wl.samples_per_step * args.steps / (total_ms * 1e-3)
-        bits = dict(ctl.quantizer.bits) if gact.config.compress_activation else {}
-        hist = {}
-        for b in bits.values():
-            hist[str(b)] = hist.get(str(b), 0) + 1
-        line = {"metric": f"GACT {wl.name} samples/s", "value": round(value, 2), "unit": "samples/s", "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 3),
-                "median_ms_per_step": round(statistics.median(per_step), 3), "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": wl.describe.get("autocast", "fp32"), "data": "synthetic",
-                "config": dict(wl.describe, workload=wl.name, level=args.level, rng=args.rng, dp_probe=args.dp_probe,
+        line = {"metric": f"GACT {res['name']} samples/s", "value": res["samples_per_s"], "unit": "samples/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
+                "median_ms_per_step": res["median_ms_per_step"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": res["describe"].get("autocast", "fp32"), "data": "synthetic",
+                "config": dict(res["describe"], workload=res["name"], level=args.level, rng=args.rng, dp_probe=args.dp_probe,
                                parallelism=f"dp{world}", ddp_bucket_mb=args.bucket_mb),
-                "compressed_tensors": len(bits), "bit_histogram": hist, "adapt_seconds": round(adapt_s, 2),
-                "peak_mem_GB": round(peak_mem / 2**30, 2), "final_loss": float(loss),
-                "gpu_launches": launches, "clocks": clocks}
+                "compressed_tensors": res["compressed_tensors"], "bit_histogram": res["bit_histogram"],
+                "adapt_seconds": res["adapt_seconds"], "peak_mem_GB": res["peak_mem_GB"], "final_loss": res["final_loss"],
+                "gpu_launches": res["gpu_launches"], "clocks": res["clocks"]}
+        if reference:
+            line["impl"] = "reference"
+            line["config"]["code"] = "the reference's gact package and CUDA extensions, unmodified (oracle/_ref/pkg)"
+        if "memory" in res:
+            line["memory"] = res["memory"]
+        if ladder is not None:
+            line["batch_ladder"] = ladder
         emit(line)
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
+
+
+def memory_ladder(args, dev, reference):
+    """Batch ladder of `workloads.batch_ladder` for the current level: doubles the batch while the next rung is
+    predicted to stay below 90 % of the device memory."""
+    import workloads
+    gact = import_gact(reference)
+    from gact.controller import Controller
+    total = torch.cuda.get_device_properties(dev).total_memory
+    kw = {}
+    if args.autocast is not None:
+        kw["autocast"] = AUTOCAST[args.autocast]
+
+    def build(batch):
+        wl = workloads.BUILDERS[args.workload](dev, batch=batch, **kw)
+        ctl = Controller(wl.model)
+        ctl.install_hook()
+        return wl, (lambda: ctl.iterate(wl.backprop)), ctl.uninstall_hook
+
+    start = args.batch or {"bert_large": 64, "resnet50": 256}[args.workload]
+    return workloads.batch_ladder(build, start, int(0.9 * total))
+
+
+# ----------------------------------------------------------------------------------------------------------------
+def run_case(args):
+    """One quantize + dequantize case (or the mask kernels) a few times, for use under a profiler.  The tensor should be
+    larger than L2 (126 MB on B200) for DRAM counters to mean anything and small enough for a multi-pass capture to
+    finish quickly (a few hundred MB).  Prints the CUDA-event time of every launch."""
+    from gact import _native as nv
+    torch.manual_seed(0)
+    s = torch.cuda.current_stream().cuda_stream
+    if args.case == "mask":
+        x = (torch.rand(args.numel, device="cuda") < 0.9).to(torch.uint8)
+        n = x.numel()
+        words = torch.empty(nv.lib.gact_mask_words(n), dtype=torch.int32, device="cuda")
+        out = torch.empty_like(x)
+        by = n + words.numel() * 4
+        for r in range(args.reps):
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            assert nv.lib.gact_mask_pack(x.data_ptr(), n, words.data_ptr(), None, s) == 0
+            e[1].record()
+            assert nv.lib.gact_mask_unpack(words.data_ptr(), n, out.data_ptr(), s) == 0
+            e[2].record()
+            torch.cuda.synchronize()
+            tp, tu = e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+            print(f"rep {r}: mask pack {tp*1e3:.1f} us ({by/tp/1e6:.0f} GB/s)  unpack {tu*1e3:.1f} us ({by/tu/1e6:.0f} GB/s)  "
+                  f"algorithmic bytes per launch {by}")
+        assert torch.equal(out, x)
+        return
+    dname, bits, rng = args.case.split(":")
+    dt, bits = DTYPES[dname], int(bits)
+    x = torch.randn(args.numel, device="cuda")
+    if args.relu:
+        x.clamp_min_(0)
+    x = x.to(dt)
+    n = x.numel()
+    G = (n + 255) // 256
+    pk = torch.empty(nv.lib.gact_packed_bytes(n, bits), dtype=torch.uint8, device="cuda")
+    mn = torch.empty(G, dtype=dt, device="cuda")
+    sc = torch.empty(G, dtype=torch.float32 if dt == torch.bfloat16 else dt, device="cuda")
+    out = torch.empty_like(x)
+    es = x.element_size()
+    by = n * es + pk.numel() + G * (es + sc.element_size())
+    for r in range(args.reps):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        st = nv.lib.gact_quantize(x.data_ptr(), nv.DTYPE_CODE[dt], n, bits, r, nv.RNG_CODE[rng], None, 1, pk.data_ptr(),
+                                  mn.data_ptr(), sc.data_ptr(), s)
+        assert st == 0
+        e[1].record()
+        st = nv.lib.gact_dequantize(pk.data_ptr(), mn.data_ptr(), sc.data_ptr(), nv.DTYPE_CODE[dt], n, bits, out.data_ptr(), s)
+        assert st == 0
+        e[2].record()
+        torch.cuda.synchronize()
+        tq, td = e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+        print(f"rep {r}: quantize {tq*1e3:.1f} us ({by/tq/1e6:.0f} GB/s)  dequantize {td*1e3:.1f} us ({by/td/1e6:.0f} GB/s)  "
+              f"algorithmic bytes per launch {by}")
 
 
 _RESULT_FD = None
@@ -610,10 +807,9 @@ def emit(line):
 
 
 def main():
-    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 200 for the sweep, 20 for training)")
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 20 for the sweep and for training)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rng", default="fast", choices=["curand", "fast", "rtn"])
@@ -621,15 +817,29 @@ def main():
     ap.add_argument("--level", default="L2", help="optimisation level of the training workloads (L0 = uncompressed)")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch of the training workloads (0 = the workload's own)")
     ap.add_argument("--layers", type=int, default=0, help="bert_large only: fewer encoder layers for quick runs")
+    ap.add_argument("--autocast", default=None, choices=["bf16", "fp16", "off"], help="autocast type of the training workloads (default: the workload's own)")
     ap.add_argument("--dp-probe", default="allreduce", choices=["allreduce", "local"])
     ap.add_argument("--bucket-mb", type=int, default=100, help="DDP gradient bucket size of the training workloads")
+    ap.add_argument("--get-mem", action="store_true", help="training workloads: activation memory of a step and a batch ladder")
     ap.add_argument("--e2e-steps", type=int, default=8)
+    ap.add_argument("--passes", type=int, default=0, help="sweep passes per step (0 = as many as make the timed region last --min-region-ms)")
+    ap.add_argument("--min-region-ms", type=float, default=1000.0)
+    ap.add_argument("--no-train", action="store_true", help="sweep only: leave out the BERT-large training runs")
+    ap.add_argument("--train-steps", type=int, default=20)
+    ap.add_argument("--train-mem", action="store_true", help="add the activation-memory readings to the `train` object")
     ap.add_argument("--no-table", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, help="DTYPE:BITS:RNG (e.g. f16:2:fast) or `mask`: run one kernel case --reps times and print its times")
+    ap.add_argument("--numel", type=int, default=1 << 27)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--relu", action="store_true")
     args = ap.parse_args()
+    if args.case is not None:
+        return run_case(args)
+    claim_stdout()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.steps is None:
-        args.steps = 20 if args.workload != "sweep" else (200 if args.impl == "ours" else 5)
+        args.steps = 5 if (args.impl == "reference" and args.workload == "sweep") else 20
     if args.workload != "sweep":
         if not torch.cuda.is_available():
             raise SystemExit("training workloads need a CUDA device")

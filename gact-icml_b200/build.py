@@ -56,6 +56,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         cmd = ["nvcc", "-shared", "-o", str(OUT)] + [str(o) for o in objs] + ["-gencode", "arch=compute_100a,code=sm_100a"]
         subprocess.check_call(cmd)
     build_fastcall(force)
+    build_hooks(force)
     return OUT
 
 
@@ -76,6 +77,32 @@ def build_fastcall(force: bool = False):
         print("fastcall module not built:", r.stderr.strip().splitlines()[-1] if r.stderr.strip() else r.returncode)
         return None
     return FASTCALL
+
+
+HOOKS = HERE / "gact" / "_hooks.so"
+
+
+def build_hooks(force: bool = False):
+    """The native fast path of the saved-tensor hooks (csrc/hooks.cpp): host C++ against libtorch, calling
+    libgact_b200.so beside it through the C ABI.  Optional: without it the hooks run their Python implementation.
+    Returns the path, or None when the compile failed."""
+    src = CSRC / "hooks.cpp"
+    if not (force or _stale(HOOKS, [src, OUT] + sorted(INCLUDE.glob("*.h")))):
+        return HOOKS
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+    incs = [f"-I{p}" for p in ce.include_paths("cuda")] + [f"-I{sysconfig.get_paths()['include']}", f"-I{INCLUDE}"]
+    libs = [f"-L{p}" for p in ce.library_paths("cuda")] + ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch", "-ltorch_python"]
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}"] + incs + [str(src), "-o", str(HOOKS)] + libs + \
+          [f"-L{OUT.parent}", "-l:" + OUT.name, "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode:
+        print("hooks module not built:", r.stderr.strip().splitlines()[-1] if r.stderr.strip() else r.returncode)
+        return None
+    return HOOKS
 
 
 if __name__ == "__main__":

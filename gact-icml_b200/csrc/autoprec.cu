@@ -14,7 +14,7 @@ namespace gact {
 // Stage 2: one block adds the partials in a fixed order.  No atomics, so the result is reproducible.
 // ---------------------------------------------------------------------------------------------------
 constexpr int kSThreads = 256;
-constexpr int kSBlocks = kSMs * 4;
+constexpr int kSBlocks = 592;             // fixed reduction grid (4 blocks for each of a B200's 148 SMs): it sizes the scratch
 
 __device__ __forceinline__ void block_sum3(double& a, double& b, double& c, double* out3) {
     __shared__ double sh[3][kSThreads / 32];
@@ -222,7 +222,6 @@ constexpr int kNoAllocPartialBytes = ((kSBlocks * 3 * (int)sizeof(double) + 255)
 constexpr int kNoAllocTableBytes = GACT_NOALLOC_MAX_SEGMENTS * 8;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartialBytes + 3 * kNoAllocTableBytes];
 
-constexpr int kMaxDevices = 64;
 static void* g_noalloc_addr[kMaxDevices];          // device address of g_noalloc_scratch, per device ordinal
 static std::mutex g_noalloc_mutex;
 
@@ -272,6 +271,17 @@ extern "C" int gact_sq_diffs3_noalloc(const float* g0, const float* g1, const fl
     if (nseg == 0 && !g2) return GACT_ERR_NULL;
     if (nseg > 0 && (!seg_ptr_host || !seg_off_host || !seg_len_host)) return GACT_ERR_NULL;
     if ((uintptr_t)out3 & 7) return GACT_ERR_ALIGN;
+    // the tables are host memory here, so they can be checked before anything is launched: the segments must
+    // tile [0, P) in order, without gaps or overlap (the kernel indexes them without further bounds tests)
+    if (nseg > 0) {
+        int64_t expect = 0;
+        for (int k = 0; k < nseg; k++) {
+            if (seg_ptr_host[k] == nullptr) return GACT_ERR_NULL;
+            if (seg_len_host[k] < 0 || seg_off_host[k] != expect) return GACT_ERR_SIZE;
+            expect += seg_len_host[k];
+        }
+        if (expect != P) return GACT_ERR_SIZE;
+    }
     unsigned char* base = nullptr;
     const int rc = noalloc_scratch_address(&base);
     if (rc != GACT_OK) return rc;

@@ -26,7 +26,7 @@ struct DequantArgs {
     const void* qscale;
     int64_t n, G, R;
     void* out;
-    int aligned32;
+    int align;               // guaranteed alignment of out in bytes: 32, 16, or 0 (element-aligned only)
 };
 
 // 2^23 + (byte `idx` of w) as a float bit pattern: bytes {w[idx], 0x00, 0x00, 0x4B}
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kDThreads) dequantize_kernel(const DequantArgs
             // this group's codes as bytes: (w >> ni*BITS) & mask, four elements per word
             const uint32_t c_lo = (BITS == 8) ? lo[u] : ((lo[u] >> (ni * BITS)) & MASK4);
             const uint32_t c_hi = (BITS == 8) ? hi[u] : ((hi[u] >> (ni * BITS)) & MASK4);
-            const bool full = (g + 1) * kGroup <= a.n;
+            const bool full = (g + 1) * kGroup <= a.n && a.align >= 16;        // else element by element
 
             if (DT == GACT_F16) {
                 // q = round_h(code * r), out = round_h(q + m): two elements per instruction after the multiply
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(kDThreads) dequantize_kernel(const DequantArgs
                     store_group8_slow<DT>(a.out, a.n, g, lane, o);
                 } else if (DT == GACT_F32) {
                     float* p = (float*)a.out + g * kGroup + lane * 8;
-                    if (a.aligned32) {
+                    if (a.align >= 32) {
                         const uint32_t w[8] = {__float_as_uint(o[0]), __float_as_uint(o[1]), __float_as_uint(o[2]), __float_as_uint(o[3]),
                                                __float_as_uint(o[4]), __float_as_uint(o[5]), __float_as_uint(o[6]), __float_as_uint(o[7])};
                         st_stream_u8(p, w);
@@ -168,7 +168,7 @@ template <int DT, int BITS, int TG> static int launch_dequantize_tile(const Dequ
     constexpr int U = (WPT >= TG) ? 1 : TG / WPT;
     const int64_t tiles = (a.R + U - 1) / U;
     const int64_t want = (tiles + kDThreads / 32 - 1) / (kDThreads / 32);
-    const int64_t cap = (int64_t)kSMs * 16;
+    const int64_t cap = (int64_t)sm_count() * 16;
     const int blocks = (int)(want < cap ? want : cap);
     dequantize_kernel<DT, BITS, TG><<<blocks, kDThreads, 0, s>>>(a);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
@@ -179,7 +179,7 @@ template <int DT, int BITS, int TG> static int launch_dequantize_tile(const Dequ
 // 16 groups per warp (8 for fp32, whose stores are twice as wide) once that leaves half a resident wave of warps,
 // else 8, else 4.
 template <int DT, int BITS> static int launch_dequantize(const DequantArgs& a, cudaStream_t s) {
-    constexpr int64_t kHalfWave = (int64_t)kSMs * 32;         // warps: half of 148 SMs x 64 resident warps
+    const int64_t kHalfWave = (int64_t)sm_count() * 32;       // warps: half of what the SMs hold (64 resident warps each)
     constexpr int kBig = (DT == GACT_F32) ? 8 : 16;
     if (a.G >= kBig * kHalfWave) return launch_dequantize_tile<DT, BITS, kBig>(a, s);
     if (kBig > 8 && a.G >= 8 * kHalfWave) return launch_dequantize_tile<DT, BITS, 8>(a, s);
@@ -207,13 +207,14 @@ extern "C" int gact_dequantize(const void* packed, const void* qmin, const void*
     if (n < 0) return GACT_ERR_SIZE;
     if (n == 0) return GACT_OK;
     if (!packed || !qmin || !qscale || !out) return GACT_ERR_NULL;
-    if (((uintptr_t)packed & 15) || ((uintptr_t)out & 15)) return GACT_ERR_ALIGN;
+    // out only has to be aligned to its element size (e.g. a view into a larger buffer); packed keeps its vector alignment
+    if (((uintptr_t)packed & 15) || ((uintptr_t)out & (dtype == GACT_F32 ? 3 : 1))) return GACT_ERR_ALIGN;
     DequantArgs a;
     a.packed = (const uint8_t*)packed; a.qmin = qmin; a.qscale = qscale; a.n = n;
     a.G = (n + kGroup - 1) / kGroup;
     a.R = (a.G + 8 / bits - 1) / (8 / bits);
     a.out = out;
-    a.aligned32 = ((uintptr_t)out & 31) ? 0 : 1;
+    a.align = ((uintptr_t)out & 15) ? 0 : (((uintptr_t)out & 31) ? 16 : 32);
     cudaStream_t s = (cudaStream_t)stream;
     switch (dtype) {
     case GACT_F32: return dispatch_dq<GACT_F32>(a, bits, s);

@@ -6,13 +6,28 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "gact_b200.h"
 
 namespace gact {
 
 constexpr int kGroup = GACT_GROUP_SIZE;   // elements per quantization group
-constexpr int kSMs = 148;                 // B200
 constexpr unsigned kFull = 0xffffffffu;
+constexpr int kMaxDevices = 64;
+
+// Number of SMs of the current device (148 on a B200), asked of the runtime once per device and cached.
+static inline int sm_count() {
+    static std::atomic<int> cached[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 
 // ---------------------------------------------------------------------------------------------------
 // Philox4x32-10 (Salmon et al., SC'11).  Ten rounds; round r uses the key bumped r times by the Weyl
@@ -161,15 +176,16 @@ template <int DT> struct RawRegs { static constexpr int N = (DT == GACT_F32) ? 8
 
 // The 8 values of group `g` that belong to `lane`, in storage format (fp32: 8 words; 16-bit: 4 packed pairs).
 // Elements at or past n read as +0 (the reference pads with real zeros, gact/gact/ops.py:12-19).
-// `aligned32`: the base pointer is 32-byte aligned (needed by the 256-bit fp32 load).
+// `align`: what the base pointer is known to be aligned to: 32 (the 256-bit fp32 load), 16 (128-bit loads), or
+// anything less (element by element, for contiguous views that start at an odd offset of their storage).
 template <int DT>
-__device__ __forceinline__ void load_raw(const void* x, int64_t n, int64_t g, int lane, bool aligned32,
+__device__ __forceinline__ void load_raw(const void* x, int64_t n, int64_t g, int lane, int align,
                                          uint32_t (&raw)[RawRegs<DT>::N]) {
     const int64_t base = g * kGroup;
-    if (base + kGroup <= n) {
+    if (base + kGroup <= n && align >= 16) {
         if constexpr (DT == GACT_F32) {
             const float* p = (const float*)x + base + lane * 8;
-            if (aligned32) {
+            if (align >= 32) {
                 ld_stream_u8(p, raw);
             } else {
                 const uint4 a = ld_stream_u4(p), b = ld_stream_u4(p + 4);
@@ -214,7 +230,7 @@ __device__ __forceinline__ void raw_to_float(const uint32_t (&raw)[RawRegs<DT>::
 template <int DT>
 __device__ __forceinline__ void load_group8(const void* x, int64_t n, int64_t g, int lane, float (&v)[8]) {
     uint32_t raw[RawRegs<DT>::N];
-    load_raw<DT>(x, n, g, lane, false, raw);
+    load_raw<DT>(x, n, g, lane, 16, raw);
     raw_to_float<DT>(raw, v);
 }
 

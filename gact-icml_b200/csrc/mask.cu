@@ -42,10 +42,10 @@ __device__ __forceinline__ uint32_t nonzero_bits16(const uint32_t (&q)[4]) {
     return m;
 }
 
-// the 16 bytes of one lane in block blk (zero past the end of the tensor)
-__device__ __forceinline__ void load_mask16(const uint8_t* __restrict__ x, int64_t n, int64_t blk, int lane, uint32_t (&q)[4]) {
+// the 16 bytes of one lane in block blk (zero past the end of the tensor); `vec`: x is 16-byte aligned
+__device__ __forceinline__ void load_mask16(const uint8_t* __restrict__ x, int64_t n, int64_t blk, int lane, bool vec, uint32_t (&q)[4]) {
     const int64_t base = blk * 512 + lane * 16;
-    if (blk * 512 + 512 <= n) {
+    if (vec && blk * 512 + 512 <= n) {
         const uint4 v = ld_stream_u4(x + base);
         q[0] = v.x; q[1] = v.y; q[2] = v.z; q[3] = v.w;
     } else {
@@ -64,7 +64,7 @@ __device__ __forceinline__ void load_mask16(const uint8_t* __restrict__ x, int64
 // A warp takes two 512-element blocks per step: lane k reads its 16 consecutive bytes of each, reduces them to
 // 16 + 16 bits, and one bit-matrix transpose across the warp turns the 32 rows into the 32 words of the two
 // blocks (lane j < 16: word j of the first block, lane 16 + j: word j of the second), written as one 128-byte row.
-__global__ void __launch_bounds__(kMThreads) mask_pack_kernel(const uint8_t* __restrict__ x, int64_t n, uint32_t* __restrict__ words,
+__global__ void __launch_bounds__(kMThreads) mask_pack_kernel(const uint8_t* __restrict__ x, int64_t n, bool vec, uint32_t* __restrict__ words,
                                                               int64_t nwords, int* not_binary) {
     const int lane = threadIdx.x & 31;
     const int64_t nblk = (n + 511) / 512;
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kMThreads) mask_pack_kernel(const uint8_t* __r
         for (int b = 0; b < 4; b++) {
             const int64_t blk = 4 * step + b;
             if (blk < nblk) {
-                load_mask16(x, n, blk, lane, q[b]);
+                load_mask16(x, n, blk, lane, vec, q[b]);
             } else {
                 q[b][0] = q[b][1] = q[b][2] = q[b][3] = 0;
             }
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(kMThreads) mask_pack_kernel(const uint8_t* __r
 }
 
 __global__ void __launch_bounds__(kMThreads) mask_unpack_kernel(const uint32_t* __restrict__ words, int64_t n, int64_t nwords,
-                                                                uint8_t* __restrict__ out) {
+                                                                uint8_t* __restrict__ out, bool vec) {
     const int lane = threadIdx.x & 31;
     const int64_t nblk = (n + 511) / 512;
     const int64_t npair = (nblk + 1) / 2;
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kMThreads) mask_unpack_kernel(const uint32_t* 
 #pragma unroll
                 for (int w = 0; w < 4; w++) q[w] = (((m >> (4 * w)) & 0xfu) * 0x00204081u) & 0x01010101u;   // bit i -> byte i
                 const int64_t base = blk * 512 + lane * 16;
-                if (blk * 512 + 512 <= n) {
+                if (vec && blk * 512 + 512 <= n) {
                     st_stream_u4(out + base, make_uint4(q[0], q[1], q[2], q[3]));
                 } else {
 #pragma unroll
@@ -146,7 +146,7 @@ using namespace gact;
 static int mask_blocks(int64_t n, int blocks_per_step) {
     const int64_t nstep = ((n + 511) / 512 + blocks_per_step - 1) / blocks_per_step;   // warp steps in all
     const int64_t want = (nstep + kMThreads / 32 - 1) / (kMThreads / 32);
-    const int64_t cap = (int64_t)kSMs * 8;
+    const int64_t cap = (int64_t)sm_count() * 8;
     return (int)(want < cap ? want : cap);
 }
 
@@ -156,8 +156,9 @@ extern "C" int gact_mask_pack(const uint8_t* x, int64_t n, uint32_t* words, int*
     if (n < 0) return GACT_ERR_SIZE;
     if (n == 0) return GACT_OK;
     if (!x || !words) return GACT_ERR_NULL;
-    if (((uintptr_t)x & 15) || ((uintptr_t)words & 3)) return GACT_ERR_ALIGN;
-    mask_pack_kernel<<<mask_blocks(n, 4), kMThreads, 0, (cudaStream_t)stream>>>(x, n, words, (n + 511) / 512 * 16, not_binary);
+    if ((uintptr_t)words & 3) return GACT_ERR_ALIGN;
+    const bool vec = ((uintptr_t)x & 15) == 0;          // a byte tensor may start anywhere; 16-byte loads where it allows
+    mask_pack_kernel<<<mask_blocks(n, 4), kMThreads, 0, (cudaStream_t)stream>>>(x, n, vec, words, (n + 511) / 512 * 16, not_binary);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }
 
@@ -165,7 +166,8 @@ extern "C" int gact_mask_unpack(const uint32_t* words, int64_t n, uint8_t* out, 
     if (n < 0) return GACT_ERR_SIZE;
     if (n == 0) return GACT_OK;
     if (!words || !out) return GACT_ERR_NULL;
-    if (((uintptr_t)out & 15) || ((uintptr_t)words & 3)) return GACT_ERR_ALIGN;
-    mask_unpack_kernel<<<mask_blocks(n, 4), kMThreads, 0, (cudaStream_t)stream>>>(words, n, (n + 511) / 512 * 16, out);
+    if ((uintptr_t)words & 3) return GACT_ERR_ALIGN;
+    const bool vec = ((uintptr_t)out & 15) == 0;
+    mask_unpack_kernel<<<mask_blocks(n, 4), kMThreads, 0, (cudaStream_t)stream>>>(words, n, (n + 511) / 512 * 16, out, vec);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }

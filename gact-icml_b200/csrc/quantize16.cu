@@ -1,0 +1,577 @@
+// Fused quantize for fp16 / bf16 inputs: per-group min/max -> scale -> stochastic rounding -> bit packing, one
+// pass over the input in HBM.
+//
+// Work decomposition.  A warp owns a tile of 8 consecutive groups (4 KB of input); each lane owns 8 consecutive
+// values (16 bytes) of every group, so a group is one fully coalesced 512-byte row and a lane's 8 packed bytes of a
+// row-block are contiguous (one 8-byte store).
+//
+// Input staging.  Every warp runs its own two-stage ring in shared memory: its elected lane brings the warp's next
+// tile in with one cp.async.bulk (the TMA engine; a plain 1-D copy of this GPU's own memory, no multicast, no
+// cluster) that completes on the stage's mbarrier, while the warp works on the current tile.  Nothing is shared
+// between warps, so there is no producer warp and no block-wide barrier; 24 warps per SM keep up to 192 KB of
+// loads in flight without holding them in registers.  The tile is read from shared memory twice (min/max pass,
+// code pass), which keeps the routine below 80 registers.  Every wait is bounded: a wait that runs out records an
+// error (gact_pipeline_error), the warp waits - bounded again - for its other copy in flight, and leaves.
+// Tiles the bulk copies cannot take (the ragged last tile, and the whole tensor when x is not 16-byte aligned)
+// are read straight from global memory, element by element where they must be.
+//
+// Tile routine.
+//   pass 1  two-wide min / max over the lane's four packed pairs, folded into one word (min, -max); the eight
+//           words of the tile are reduced across the warp together by a butterfly that halves the number of live
+//           words with every exchange (9 shuffles for 8 groups instead of 16 single-group reductions); lanes
+//           4k..4k+3 end up with group k's pair, compute its scale and write min / scale.
+//           fp16 scale: the reference's double-precision quotient rounded to float and then to half is taken from
+//           an fp32 reciprocal whenever that cannot change the result (quotient further than 16 fp32 ulps from
+//           every half-precision rounding boundary, checked on the bit pattern); the double-precision path
+//           remains for the other ~0.4 % of the groups.
+//   pass 2  (x - min) * scale in two-wide half arithmetic with the reference's roundings (fp16), or one
+//           mixed-precision subtract and a packed fma in fp32 (bf16); noise added in fp32; w + 1.5*2^23 leaves
+//           rint(w) in the low mantissa bits (no conversion instruction); slots are summed with shifted adds and
+//           the bytes cut out with byte permutes.  fp16 round-to-nearest never leaves half precision: p + 1024
+//           rounds to the integer in the low mantissa bits of each half and two codes travel per instruction.
+#include <atomic>
+
+#include "quantize_common.cuh"
+
+namespace gact {
+
+constexpr int kTG = 8;                               // groups per warp tile
+constexpr int kTileElems = kTG * kGroup;             // 2048
+constexpr int kTileBytes = kTileElems * 2;           // 4096
+#ifndef GACT_Q16_STAGES
+#define GACT_Q16_STAGES 2
+#endif
+#ifndef GACT_Q16_MINB
+#define GACT_Q16_MINB 3
+#endif
+constexpr int kStages = GACT_Q16_STAGES;
+constexpr int kWarps = kQThreads / 32;
+constexpr int kSmemBytes = kWarps * kStages * kTileBytes;   // 64 KB per block, 3 blocks per SM
+
+__device__ int g_pipeline_error = 0;
+
+// ---- two-wide helpers on the bit patterns of half2 / bfloat162 --------------------------------------------------
+template <int DT> __device__ __forceinline__ uint32_t pmin2(uint32_t a, uint32_t b) {
+    if constexpr (DT == GACT_F16) {
+        const __half2 r = __hmin2(*(const __half2*)&a, *(const __half2*)&b);
+        return *(const uint32_t*)&r;
+    } else {
+        const __nv_bfloat162 r = __hmin2(*(const __nv_bfloat162*)&a, *(const __nv_bfloat162*)&b);
+        return *(const uint32_t*)&r;
+    }
+}
+template <int DT> __device__ __forceinline__ uint32_t pmax2(uint32_t a, uint32_t b) {
+    if constexpr (DT == GACT_F16) {
+        const __half2 r = __hmax2(*(const __half2*)&a, *(const __half2*)&b);
+        return *(const uint32_t*)&r;
+    } else {
+        const __nv_bfloat162 r = __hmax2(*(const __nv_bfloat162*)&a, *(const __nv_bfloat162*)&b);
+        return *(const uint32_t*)&r;
+    }
+}
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *(const __half2*)&v; }
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *(const uint32_t*)&v; }
+template <int DT> __device__ __forceinline__ float pair_lo(uint32_t v) {
+    if constexpr (DT == GACT_F16) return __half2float(__ushort_as_half((unsigned short)(v & 0xffffu)));
+    else return __uint_as_float(v << 16);
+}
+template <int DT> __device__ __forceinline__ float pair_hi(uint32_t v) {
+    if constexpr (DT == GACT_F16) return __half2float(__ushort_as_half((unsigned short)(v >> 16)));
+    else return __uint_as_float(v & 0xffff0000u);
+}
+// (hi, hi) with hi = the reference's start value 1e30 in T (half: +inf)
+template <int DT> __device__ __forceinline__ uint32_t start_pair() { return DT == GACT_F16 ? 0x7c007c00u : 0x714a714au; }
+
+// (min, -max) of the lane's 8 values; NaN values are ignored (an all-NaN lane yields NaN, ignored further on)
+template <int DT> __device__ __forceinline__ uint32_t lane_min_negmax(const uint32_t (&raw)[4]) {
+    const uint32_t lo = pmin2<DT>(pmin2<DT>(raw[0], raw[1]), pmin2<DT>(raw[2], raw[3]));
+    const uint32_t hi = pmax2<DT>(pmax2<DT>(raw[0], raw[1]), pmax2<DT>(raw[2], raw[3]));
+    const uint32_t nh = hi ^ 0x80008000u;
+    return pmin2<DT>(__byte_perm(lo, nh, 0x5410u), __byte_perm(lo, nh, 0x7632u));
+}
+
+// Warp reduction of the tile's eight (min, -max) words at once.  Exchanges at distance 16, 8 and 4 each halve the
+// number of words a lane still carries (a lane keeps the groups whose index bit matches its lane bit and hands the
+// others over); distances 2 and 1 finish the remaining word.  Lanes 4k .. 4k+3 return group k's word.
+template <int DT> __device__ __forceinline__ uint32_t tile_reduce(uint32_t (&v)[kTG], int lane) {
+    {
+        const bool up = (lane & 16) != 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t keep = up ? v[i + 4] : v[i], send = up ? v[i] : v[i + 4];
+            v[i] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, 16));
+        }
+    }
+    {
+        const bool up = (lane & 8) != 0;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint32_t keep = up ? v[i + 2] : v[i], send = up ? v[i] : v[i + 2];
+            v[i] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, 8));
+        }
+    }
+    {
+        const bool up = (lane & 4) != 0;
+        const uint32_t keep = up ? v[1] : v[0], send = up ? v[0] : v[1];
+        v[0] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, 4));
+    }
+    v[0] = pmin2<DT>(v[0], __shfl_xor_sync(kFull, v[0], 2));
+    v[0] = pmin2<DT>(v[0], __shfl_xor_sync(kFull, v[0], 1));
+    return v[0];
+}
+
+// scale of an fp16 group, T(double(T(2^b - 1)) / (double(T(mx - mn)) + 2e-6)) with T reached through float
+// (quantization_cuda_kernel.cu:33), from an fp32 reciprocal where the two roundings cannot tell the difference.
+template <int BITS> __device__ __forceinline__ float scale_f16(float mn, float mx) {
+    constexpr float MAXC = (float)((1 << BITS) - 1);
+    const float r = Elem<GACT_F16>::round(__fsub_rn(mx, mn));
+    float rcp;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(__fadd_rn(r, 2e-6f)));
+    float q = MAXC * rcp;                                  // within 4 fp32 ulps of the double-precision quotient
+    // The result is half(float(quotient)).  Half-precision rounding boundaries are the fp32 values whose low 13
+    // mantissa bits read 0x1000; an estimate at least 16 ulps away from all of them rounds like the exact quotient
+    // (this holds for results in the normal half range and above it, where everything becomes +inf).
+    const uint32_t low = __float_as_uint(q) & 0x1fffu;
+    if ((low - (0x1000u - 16u)) < 32u || !(q >= 6.2e-5f))  // near a boundary, subnormal, zero, negative or NaN
+        q = __double2float_rn((double)MAXC / ((double)r + 2e-6));
+    return Elem<GACT_F16>::round(q);
+}
+
+// ---- sources of a tile's values ----------------------------------------------------------------------------------
+// the warp's stage in shared memory; `base` already points at this lane's 16 bytes of group 0
+struct SmemSrc {
+    const unsigned char* base;
+    __device__ __forceinline__ void load(int k, uint32_t (&raw)[4]) const {
+        const uint4 v = *(const uint4*)(base + k * (kGroup * 2));
+        raw[0] = v.x; raw[1] = v.y; raw[2] = v.z; raw[3] = v.w;
+    }
+    __device__ __forceinline__ uint32_t load_pair(int k, int i) const { return *(const uint32_t*)(base + k * (kGroup * 2) + i * 4); }
+};
+// global memory, bounds-checked; elements at or past n (and whole groups at or past G) read as +0
+template <int DT> struct GlobalSrc {
+    const void* x;
+    int64_t n, g0;
+    int lane, align;
+    __device__ __forceinline__ void load(int k, uint32_t (&raw)[4]) const { load_raw<DT>(x, n, g0 + k, lane, align, raw); }
+    __device__ __forceinline__ uint32_t load_pair(int k, int i) const {
+        uint32_t raw[4];
+        load(k, raw);
+        return raw[i];
+    }
+};
+
+// ---- codes of one pair of elements, as magic bits (1.5*2^23 + code) ------------------------------------------------
+// fp16: the reference's half-precision arithmetic, p = round_h(round_h(x - mn) * scale), max(p, 0) (NaN -> 0), no
+// upper clamp in the reference's modes (CURAND, EXTERNAL), clamp at 2^b - 1 in FAST / RTN.
+template <int BITS, int RNG>
+__device__ __forceinline__ void code_pair_f16(uint32_t rawp, uint32_t mn2, uint32_t sc2, float2 nz, uint32_t& c0, uint32_t& c1) {
+    constexpr float MAXC = (float)((1 << BITS) - 1);
+    const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
+    const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
+    __half2 p = __hmax2(__hmul2(t, as_h2(sc2)), zero2);
+    if (NoOverflow<RNG>::value) p = __hmin2(p, maxc2);
+    float2 r;
+    if (RNG == GACT_RNG_RTN) r = add2(__half22float2(p), splat2(kMagic));                        // (p + 0.5) - 0.5 = p
+    else if (Centred<GACT_F16, RNG>::value) r = add2(mixed_add2(p, nz), splat2(kMagic));         // p + (noise - 0.5)
+    else r = add2(add2(mixed_add2(p, nz), splat2(-0.5f)), splat2(kMagic));                       // u - 0.5 >= -0.5 rounds to 0
+    c0 = __float_as_uint(r.x);
+    c1 = __float_as_uint(r.y);
+}
+// fp16 group whose scale overflowed to +inf (range below (2^b-1)/65504): the reference computes t*inf, +inf for
+// every element above the minimum, which __float2int_rn saturates to 0x7fffffff (all ones from the slot upwards),
+// and NaN -> 0 for the minimum itself.  FAST / RTN clamp at 2^b - 1 instead.
+template <int BITS, int RNG>
+__device__ __forceinline__ void code_pair_f16_inf(uint32_t rawp, uint32_t mn2, uint32_t& c0, uint32_t& c1) {
+    const float2 t = __half22float2(__hsub2(as_h2(rawp), as_h2(mn2)));
+    const uint32_t top = NoOverflow<RNG>::value ? (uint32_t)((1 << BITS) - 1) : 0x7fffffffu;
+    c0 = t.x > 0.0f ? top : 0u;
+    c1 = t.y > 0.0f ? top : 0u;
+}
+// fp16, round to nearest, staying in half precision: returns (0x6400 + code) in each half
+template <int BITS> __device__ __forceinline__ uint32_t code_pair_f16_rtn(uint32_t rawp, uint32_t mn2, uint32_t sc2, bool inf_scale) {
+    constexpr float MAXC = (float)((1 << BITS) - 1);
+    const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
+    const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
+    __half2 p;
+    if (inf_scale) p = __hmul2(__hgt2(t, zero2), maxc2);                                         // t > 0 ? 2^b - 1 : 0
+    else p = __hmin2(__hmax2(__hmul2(t, as_h2(sc2)), zero2), maxc2);
+    return h2_bits(__hadd2(p, __float2half2_rn(1024.0f)));
+}
+// bf16 (our semantics): u = fma(x - mn, scale, noise - 0.5) in fp32, clamped to [0, 2^b - 1], NaN -> 0.
+// PLAIN: the group holds no infinity (scale > 0), so NaN can only come from a NaN element, and max(x, mn) - a
+// two-wide instruction that ignores NaN - sends those to the minimum, i.e. to code 0, like the clamp does; the
+// lower clamp is then implied (u >= -0.5 rounds to 0).
+template <int BITS, int RNG, bool PLAIN>
+__device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, float nmn, float sc, float2 nz, uint32_t& c0, uint32_t& c1) {
+    constexpr float MAXC = (float)((1 << BITS) - 1);
+    if (PLAIN) rawp = pmax2<GACT_BF16>(rawp, mn2);
+    const float2 t = mixed_add2_bf16(rawp, splat2(nmn));
+    float2 w = fma2(t, splat2(sc), nz);
+    if (!PLAIN) { w.x = fmaxf(w.x, 0.0f); w.y = fmaxf(w.y, 0.0f); }
+    if (!NoOverflow<RNG>::value) { w.x = fminf(w.x, MAXC); w.y = fminf(w.y, MAXC); }
+    const float2 r = add2(w, splat2(kMagic));
+    c0 = __float_as_uint(r.x);
+    c1 = __float_as_uint(r.y);
+}
+
+// what every lane needs to know about one group in pass 2
+template <int DT> struct GroupConst;
+template <> struct GroupConst<GACT_F16> {
+    uint32_t mn2, sc2;
+    bool special;                                   // scale is +inf
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t, int src) {
+        const uint32_t w = __shfl_sync(kFull, w0, src);
+        mn2 = __byte_perm(w, w, 0x1010u);
+        sc2 = __byte_perm(w, w, 0x3232u);
+        special = ((w >> 16) & 0x7fffu) == 0x7c00u;
+    }
+};
+template <> struct GroupConst<GACT_BF16> {
+    uint32_t mn2;
+    float nmn, sc;
+    bool special;                                   // not (scale > 0): the group holds an infinity, or only NaN
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src) {
+        const uint32_t m = __shfl_sync(kFull, w0, src);
+        sc = __uint_as_float(__shfl_sync(kFull, w1, src));
+        mn2 = __byte_perm(m, m, 0x3232u);
+        nmn = -__uint_as_float(m);
+        special = !(sc > 0.0f);
+    }
+};
+
+template <int DT, int BITS, int RNG, bool SPECIAL>
+__device__ __forceinline__ void code_pair_as(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
+    if constexpr (DT == GACT_F16) {
+        if (SPECIAL) code_pair_f16_inf<BITS, RNG>(rawp, gc.mn2, c0, c1);
+        else code_pair_f16<BITS, RNG>(rawp, gc.mn2, gc.sc2, nz, c0, c1);
+    } else {
+        code_pair_bf16<BITS, RNG, !SPECIAL>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
+    }
+}
+template <int DT, int BITS, int RNG>
+__device__ __forceinline__ void code_pair(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
+    if (gc.special) code_pair_as<DT, BITS, RNG, true>(rawp, gc, nz, c0, c1);
+    else code_pair_as<DT, BITS, RNG, false>(rawp, gc, nz, c0, c1);
+}
+// the eight codes of a group; the special case is decided once for the group (it is the same for the whole warp)
+template <int DT, int BITS, int RNG>
+__device__ __forceinline__ void codes8(const uint32_t (&raw)[4], const GroupConst<DT>& gc, const float2 (&nz)[4], uint32_t (&cb)[8]) {
+    if (gc.special) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, true>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, false>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+    }
+}
+
+// ---- one tile ---------------------------------------------------------------------------------------------------------
+// FULL: all 8 groups exist and are complete.
+template <int DT, int BITS, int RNG, bool FULL, class Src>
+__device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lane, const Src& src) {
+    constexpr int WPT = 8 / BITS, U = kTG / WPT;
+    const int64_t g0 = tile * kTG;
+    const int myk = lane >> 2;                              // the group whose min / max / scale this lane ends up with
+
+    // ---- pass 1: min, max, scale ----
+    uint32_t v[kTG];
+#pragma unroll
+    for (int k = 0; k < kTG; k++) {
+        uint32_t raw[4];
+        src.load(k, raw);
+        v[k] = lane_min_negmax<DT>(raw);
+    }
+    // the reference starts from +-1e30 in T, which is what remains of a group of NaNs
+    const uint32_t mnx = pmin2<DT>(tile_reduce<DT>(v, lane), start_pair<DT>());
+    float mn = pair_lo<DT>(mnx), mx = -pair_hi<DT>(mnx);
+    // a zero extreme takes the sign the reference's reduction order gives it (rare; decided per group by the whole warp)
+    const unsigned amb = __ballot_sync(kFull, zero_sign_ambiguous(mn, mx));
+    if (amb) {
+#pragma unroll
+        for (int k = 0; k < kTG; k++) {
+            if (amb & (0xFu << (4 * k))) {
+                uint32_t raw[4];
+                float vals[8];
+                src.load(k, raw);
+                raw_to_float<DT>(raw, vals);
+                const float z = zero_sign_like_reference<DT>(vals, lane);
+                if (myk == k) {
+                    if (mn == 0.0f) mn = z;
+                    if (mx == 0.0f) mx = z;
+                }
+            }
+        }
+    }
+    float sc;
+    uint32_t w0, w1 = 0;                                    // what pass 2 fetches from lane 4k
+    if constexpr (DT == GACT_F16) {
+        sc = scale_f16<BITS>(mn, mx);
+        w0 = h2_bits(__floats2half2_rn(mn, sc));            // both are half-precision values already
+    } else {
+        sc = compute_scale<DT>(mn, mx, BITS);
+        w0 = __float_as_uint(mn);
+        w1 = __float_as_uint(sc);
+    }
+    if ((lane & 3) == 0 && (FULL || g0 + myk < a.G)) {
+        if constexpr (DT == GACT_F16) {
+            ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 & 0xffffu);
+            ((unsigned short*)a.qscale)[g0 + myk] = (unsigned short)(w0 >> 16);
+        } else {
+            ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 >> 16);
+            ((float*)a.qscale)[g0 + myk] = sc;
+        }
+    }
+
+    // ---- pass 2: codes, one row-block at a time ----
+    float2 nz_odd[4];            // FAST: noise of an odd group, produced together with the even group before it
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+        const int64_t r = tile * U + u;
+        if (!FULL && r >= a.R) break;
+        uint8_t* dst = a.packed + r * kGroup + lane * 8;
+
+        if constexpr (DT == GACT_F16 && RNG == GACT_RNG_RTN) {
+            // two codes per register: every slot adds (0x6400 + code) << shift; the 0x6400s are taken out again by the
+            // start value, and what they carry across the halves cancels with it (arithmetic modulo 2^32)
+            uint32_t init = 0;
+#pragma unroll
+            for (int ni = 0; ni < WPT; ni++) init -= 0x64006400u << (ni * BITS);
+            uint32_t acc2[4] = {init, init, init, init};
+#pragma unroll
+            for (int ni = 0; ni < WPT; ni++) {
+                const int k = u * WPT + ni;
+                GroupConst<DT> gc;
+                gc.fetch(w0, w1, 4 * k);
+                uint32_t raw[4];
+                src.load(k, raw);
+                const bool present = FULL || g0 + k < a.G;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t c = present ? code_pair_f16_rtn<BITS>(raw[i], gc.mn2, gc.sc2, gc.special) : 0x64006400u;
+                    acc2[i] += c << (ni * BITS);
+                }
+            }
+            st_stream_u2(dst, make_uint2(__byte_perm(acc2[0], acc2[1], 0x6420u), __byte_perm(acc2[2], acc2[3], 0x6420u)));
+        } else if constexpr (RNG == GACT_RNG_CURAND) {
+            // the reference stream: one generator per packed byte (subsequence = byte index), slot ni = draw ni, so
+            // the work goes byte pair by byte pair: two Philox calls serve up to four slots of two bytes
+            uint32_t acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] = 0;
+            GroupConst<DT> gc[WPT];
+#pragma unroll
+            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, 4 * (u * WPT + ni));
+            const uint64_t gid0 = (uint64_t)r * kGroup + lane * 8;
+#pragma unroll
+            for (int c = 0; c < (WPT + 3) / 4; c++) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint64_t gid = gid0 + 2 * i;
+                    const uint4 ra = philox4x32_10((uint32_t)c, 0u, (uint32_t)gid, (uint32_t)(gid >> 32), a.rk);
+                    const uint4 rb = philox4x32_10((uint32_t)c, 0u, (uint32_t)(gid + 1), (uint32_t)((gid + 1) >> 32), a.rk);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int ni = c * 4 + q;
+                        if (ni >= WPT) break;
+                        const int k = u * WPT + ni;
+                        if (!FULL && g0 + k >= a.G) break;     // tail row-block: absent groups leave zero bits
+                        const float2 nz = curand_uniform2<Centred<DT, RNG>::value>(word_of(ra, q), word_of(rb, q));
+                        uint32_t c0, c1;
+                        code_pair<DT, BITS, RNG>(src.load_pair(k, i), gc[ni], nz, c0, c1);
+                        acc[2 * i] |= c0 << (ni * BITS);
+                        acc[2 * i + 1] |= c1 << (ni * BITS);
+                    }
+                }
+            }
+            st_stream_u2(dst, gather_bytes8(acc));
+        } else {
+            uint32_t acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] = 0;
+#pragma unroll
+            for (int ni = 0; ni < WPT; ni++) {
+                const int k = u * WPT + ni;
+                if (!FULL && g0 + k >= a.G) break;
+                float2 nz[4];
+                if (RNG == GACT_RNG_FAST) {
+                    if ((k & 1) == 0) {
+                        fast_noise16<true>((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) nz[i] = nz_odd[i];
+                    }
+                } else if (RNG == GACT_RNG_RTN) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) nz[i] = splat2(0.0f);
+                } else {
+                    const float2* p = (const float2*)(a.noise + (g0 + k) * kGroup + lane * 8);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) nz[i] = Centred<DT, RNG>::value ? add2(p[i], splat2(-0.5f)) : p[i];
+                }
+                GroupConst<DT> gc;
+                gc.fetch(w0, w1, 4 * k);
+                uint32_t raw[4];
+                src.load(k, raw);
+                uint32_t cb[8];
+                codes8<DT, BITS, RNG>(raw, gc, nz, cb);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (NoOverflow<RNG>::value) acc[j] += cb[j] << (ni * BITS);      // disjoint slots: a sum is an OR
+                    else acc[j] |= cb[j] << (ni * BITS);
+                }
+            }
+            st_stream_u2(dst, gather_bytes8(acc));
+        }
+    }
+}
+
+// ---- the warp-private bulk-copy ring -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// true once the phase with the given parity has completed; gives up after `limit` polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t it = 0; it < limit; ++it) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// plain 1-D bulk copy global -> this block's shared memory (no multicast), completing on `bar`
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// bulk_tiles: the leading tiles that come through the rings (0 when x is not 16-byte aligned)
+template <int DT, int BITS, int RNG>
+__global__ void __launch_bounds__(kQThreads, GACT_Q16_MINB) quantize16_kernel(const __grid_constant__ QuantArgs a, int64_t bulk_tiles) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t bars[kWarps][kStages];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t nw = (int64_t)gridDim.x * kWarps, gw = (int64_t)blockIdx.x * kWarps + warp;
+    const int64_t tiles = (a.G + kTG - 1) / kTG;
+
+    if (gw < bulk_tiles) {
+        unsigned char* buf = smem + warp * (kStages * kTileBytes);
+        const uint32_t bar0 = smem_u32(&bars[warp][0]), buf0 = smem_u32(buf);
+        const unsigned char* x = (const unsigned char*)a.x;
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < kStages; s++) mbar_init(bar0 + 8 * s, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+#pragma unroll
+            for (int s = 0; s < kStages; s++) {
+                const int64_t t = gw + s * nw;
+                if (t < bulk_tiles && !(a.withhold_copy && gw == 0 && s == 0)) {
+                    mbar_expect_tx(bar0 + 8 * s, kTileBytes);
+                    bulk_load(buf0 + s * kTileBytes, x + t * kTileBytes, kTileBytes, bar0 + 8 * s);
+                }
+            }
+        }
+        __syncwarp();
+        int64_t i = 0;
+        for (int64_t t = gw; t < bulk_tiles; t += nw, ++i) {
+            const int s = (int)(i % kStages);
+            // all lanes poll; the verdict is taken jointly so that the warp never splits
+            if (!__all_sync(kFull, mbar_wait(bar0 + 8 * s, (uint32_t)((i / kStages) & 1), a.wait_limit))) {
+                if (lane == 0) atomicExch(&g_pipeline_error, 2);
+                // do not leave while copies into the other stages may still be in flight
+#pragma unroll
+                for (int d = 1; d < kStages; d++)
+                    if (t + d * nw < bulk_tiles)
+                        mbar_wait(bar0 + 8 * (int)((i + d) % kStages), (uint32_t)(((i + d) / kStages) & 1), a.wait_limit);
+                return;
+            }
+            const SmemSrc src{buf + s * kTileBytes + lane * 16};
+            tile16<DT, BITS, RNG, true>(a, t, lane, src);
+            __syncwarp();                                        // every lane is done reading the stage
+            const int64_t tn = t + kStages * nw;
+            if (lane == 0 && tn < bulk_tiles) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(bar0 + 8 * s, kTileBytes);
+                bulk_load(buf0 + s * kTileBytes, x + tn * kTileBytes, kTileBytes, bar0 + 8 * s);
+            }
+        }
+    }
+    // what the rings do not take: the ragged end, or everything when x is not 16-byte aligned
+    for (int64_t t = bulk_tiles + gw; t < tiles; t += nw) {
+        const GlobalSrc<DT> src{a.x, a.n, t * kTG, lane, a.align};
+        tile16<DT, BITS, RNG, false>(a, t, lane, src);
+    }
+}
+
+template <int DT, int BITS, int RNG>
+static int launch16(const QuantArgs& a, cudaStream_t s) {
+    // the shared-memory opt-in is a per-device attribute of the kernel: 0 = not set up, 1 = usable, -1 = refused
+    static std::atomic<int> ready_on[kMaxDevices];
+    static std::atomic<int> per_sm_cached{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return GACT_ERR_LAUNCH;
+    int ready = ready_on[dev].load(std::memory_order_relaxed);
+    if (ready == 0) {
+        ready = cudaFuncSetAttribute(quantize16_kernel<DT, BITS, RNG>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess ? 1 : -1;
+        ready_on[dev].store(ready, std::memory_order_relaxed);
+    }
+    if (ready != 1) return GACT_ERR_LAUNCH;
+    int per_sm = per_sm_cached.load(std::memory_order_relaxed);
+    if (per_sm == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize16_kernel<DT, BITS, RNG>, kQThreads, kSmemBytes) != cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        per_sm_cached.store(per_sm, std::memory_order_relaxed);
+    }
+    const int64_t tiles = (a.G + kTG - 1) / kTG;
+    const int64_t bulk_tiles = a.align >= 16 ? a.n / kTileElems : 0;
+    const int64_t resident = (int64_t)per_sm * sm_count();
+    const int64_t want = (tiles + kWarps - 1) / kWarps;
+    const int blocks = (int)(want < resident ? want : resident);
+    quantize16_kernel<DT, BITS, RNG><<<blocks, kQThreads, kSmemBytes, s>>>(a, bulk_tiles);
+    return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+}
+
+template <int DT, int BITS>
+static int dispatch_rng16(const QuantArgs& a, int rng, cudaStream_t s) {
+    switch (rng) {
+    case GACT_RNG_CURAND: return launch16<DT, BITS, GACT_RNG_CURAND>(a, s);
+    case GACT_RNG_FAST: return launch16<DT, BITS, GACT_RNG_FAST>(a, s);
+    case GACT_RNG_RTN: return launch16<DT, BITS, GACT_RNG_RTN>(a, s);
+    case GACT_RNG_EXTERNAL: return launch16<DT, BITS, GACT_RNG_EXTERNAL>(a, s);
+    default: return GACT_ERR_MODE;
+    }
+}
+
+template <int DT>
+static int dispatch_bits16(const QuantArgs& a, int bits, int rng, cudaStream_t s) {
+    switch (bits) {
+    case 1: return dispatch_rng16<DT, 1>(a, rng, s);
+    case 2: return dispatch_rng16<DT, 2>(a, rng, s);
+    case 4: return dispatch_rng16<DT, 4>(a, rng, s);
+    case 8: return dispatch_rng16<DT, 8>(a, rng, s);
+    default: return GACT_ERR_BITS;
+    }
+}
+
+int launch_quantize16(const QuantArgs& a, int dtype, int bits, int rng, cudaStream_t s) {
+    return dtype == GACT_F16 ? dispatch_bits16<GACT_F16>(a, bits, rng, s) : dispatch_bits16<GACT_BF16>(a, bits, rng, s);
+}
+
+}  // namespace gact
+
+using namespace gact;
+
+extern "C" int gact_pipeline_error(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_pipeline_error, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+extern "C" int gact_pipeline_error_reset(void) {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_pipeline_error, &zero, sizeof(int)) == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+}

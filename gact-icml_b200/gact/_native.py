@@ -33,6 +33,8 @@ _SIGNATURES = {
     "gact_packed_bytes": ([_i64, _i], _i64),
     "gact_quantize": ([_vp, _i, _i64, _i, _u64, _i, _vp, _i, _vp, _vp, _vp, _vp], _i),
     "gact_pipeline_error": ([], _i),
+    "gact_pipeline_error_reset": ([], _i),
+    "gact_pipeline_test_hook": ([C.c_uint32, _i], None),
     "gact_dequantize": ([_vp, _vp, _vp, _i, _i64, _i, _vp, _vp], _i),
     "gact_minimax": ([_vp, _i, _i64, _vp, _vp, _vp], _i),
     "gact_mask_words": ([_i64], _i64),
@@ -44,7 +46,6 @@ _SIGNATURES = {
     "gact_sensitivity": ([_vp, _d, _vp, _i, _vp], _i),
     "gact_calc_precision": ([_vp, _vp, _vp, _i, _d, _vp, _vp], _i),
     "gact_calc_precision_host": ([_vp, _vp, _vp, _i, _d], _i),
-    "gact_set_ring_min_chunks": ([_i64], _i64),
 }
 for _name, (_args, _res) in _SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -76,6 +77,18 @@ def check(status: int, what: str) -> None:
     if status in (1, 2, 5, 6, 9):
         raise ValueError(msg)
     raise GactError(msg)
+
+
+def check_pipeline(where: str) -> None:
+    """Raise if a bounded wait of the quantize kernel's bulk-copy pipeline ever ran out on the current device:
+    the tiles that warp had not written hold stale bytes, so training must not go on as if nothing had happened.
+    Reads one word from the device (synchronises); called where the host waits anyway.  The word is cleared
+    so that the next check reports new trouble only."""
+    err = lib.gact_pipeline_error()
+    if err > 0:
+        lib.gact_pipeline_error_reset()
+        raise GactError(f"{where}: a bulk copy of gact_quantize did not arrive within its wait limit "
+                        f"(pipeline error {err}); compressed activations of this step are incomplete")
 
 
 def require_cuda(t: torch.Tensor, name: str) -> None:

@@ -132,6 +132,11 @@ class AutoPrecision:
     def _distances(self, flat0, flat1, grads, out3):
         """out3 <- (|g0-g1|^2, |g0-g2|^2, |g1-g2|^2); g2 is read in place from the live gradients."""
         dev = flat0.device
+        # The three passes must have produced gradients for the same parameters (a conditionally used parameter
+        # breaks that); the kernel indexes all three vectors with one length.
+        if not (flat0.numel() == flat1.numel() == sum(g.numel() for g in grads)):
+            raise RuntimeError("auto precision: the probe passes produced gradients of different total size "
+                               "(%d, %d, %d)" % (flat0.numel(), flat1.numel(), sum(g.numel() for g in grads)))
         if self._scratch is None or self._scratch.device != dev:
             self._scratch = torch.empty(nv.lib.gact_sq_diffs3_scratch_bytes(), dtype=torch.uint8, device=dev)
         direct = all(g.dtype == torch.float32 and g.is_contiguous() for g in grads)
@@ -198,6 +203,8 @@ class AutoPrecision:
         nv.check(st, "gact_sensitivity")
         for l, c in zip(tids, C_dev.tolist()):            # the only host synchronisation of the probe
             self.C[l] = c
+        with nv.device_guard(C_dev):
+            nv.check_pipeline("auto precision probe")     # the host has just waited for the device anyway
         self._flat = [None, None]
 
     # ------------------------------------------------------------------------------------------------

@@ -13,6 +13,12 @@ import torch
 from gact.conf import config
 from gact.quantizer import Quantizer
 from gact.autoprec import AutoPrecision
+from gact import _native as _nv
+
+
+def _device_live():
+    """True when this process has a CUDA context (asking the library about its device state would create one)."""
+    return torch.cuda.is_available() and torch.cuda.is_initialized()
 
 
 class Controller:
@@ -77,6 +83,8 @@ class Controller:
         if getattr(self, "_hook_installed", False):
             torch._C._autograd._pop_saved_tensors_default_hooks()
             self._hook_installed = False
+            if config.compress_activation and _device_live():
+                _nv.check_pipeline("Controller.uninstall_hook")
 
     def iterate(self, get_grad):
         if not config.compress_activation:

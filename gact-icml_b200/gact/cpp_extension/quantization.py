@@ -55,6 +55,11 @@ def unpack_single_precision(data, bits, scale, mn, N, num_groups, group_size):
     if bits not in (1, 2, 4, 8):
         raise ValueError("bits must be 1, 2, 4 or 8")
     n = int(N) * 256
+    # every extent the kernel reads follows from N: refuse tensors that are shorter than that
+    if data.numel() * data.element_size() < nv.lib.gact_packed_bytes(n, bits) or scale.numel() < int(N) or mn.numel() < int(N):
+        raise ValueError("data / scale / min are too small for N = %d groups at %d bits" % (int(N), bits))
+    if mn.dtype != scale.dtype:
+        raise ValueError("scale and min must have the same dtype")
     out = torch.empty((int(N), 1, 256), dtype=scale.dtype, device=data.device)
     with nv.device_guard(data):
         st = nv.lib.gact_dequantize(data.data_ptr(), mn.data_ptr(), scale.data_ptr(), _DTYPES[scale.dtype], n, bits,
@@ -79,6 +84,10 @@ def act_quantize_dropout_mask(data):
 def act_dequantize_dropout_mask(mask, N):
     _check(mask, "mask")
     n = int(N)
+    # a partial last block of 512 elements spreads over all of its 16 words: a mask of ceil(n/32) words, as the
+    # reference allocates, is too short unless n is a multiple of 512
+    if mask.numel() < nv.lib.gact_mask_words(n):
+        raise ValueError("mask holds %d words, N = %d needs %d" % (mask.numel(), n, nv.lib.gact_mask_words(n)))
     out = torch.empty(n, dtype=torch.uint8, device=mask.device)
     with nv.device_guard(mask):
         st = nv.lib.gact_mask_unpack(mask.data_ptr(), n, out.data_ptr(), nv.stream_ptr())

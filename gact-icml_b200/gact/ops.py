@@ -84,6 +84,13 @@ def dequantize_and_unpack(data, shape, q_bit, scale, mn):
         return data
     nv.require_cuda(data, "data")
     n = _numel(shape)
+    # the kernel derives every extent from n: refuse payloads that are shorter than that
+    G = (n + nv.GROUP - 1) // nv.GROUP
+    need = nv.lib.gact_packed_bytes(n, q_bit)
+    if need < 0:
+        raise ValueError("bits must be 1, 2, 4, 8 or 32, got %r" % (q_bit,))
+    if data.numel() * data.element_size() < need or scale.numel() < G or mn.numel() < G:
+        raise ValueError("compressed payload is too small for a tensor of shape %s at %d bits" % (tuple(shape), q_bit))
     out = torch.empty(tuple(int(s) for s in shape), dtype=mn.dtype, device=data.device)
     with nv.device_guard(data):
         st = nv.lib.gact_dequantize(data.data_ptr(), mn.data_ptr(), scale.data_ptr(), nv.DTYPE_CODE[mn.dtype], n, q_bit,
@@ -117,6 +124,9 @@ def op_dequantize_mask(input, dtype=torch.uint8):
     """Reference: gact/gact/ops.py:52-55."""
     q_mask, input_shape = input
     n = _numel(input_shape)
+    # a partial last block of 512 elements still spreads over all of its 16 words
+    if q_mask.numel() < nv.lib.gact_mask_words(n):
+        raise ValueError("packed mask holds %d words, %d elements need %d" % (q_mask.numel(), n, nv.lib.gact_mask_words(n)))
     out = torch.empty(tuple(int(s) for s in input_shape), dtype=torch.uint8, device=q_mask.device)
     with nv.device_guard(q_mask):
         st = nv.lib.gact_mask_unpack(q_mask.data_ptr(), n, out.data_ptr(), nv.stream_ptr())
@@ -208,6 +218,19 @@ class Packed:
         return 4
 
 
+# The native fast path of the hooks (csrc/hooks.cpp, optional) builds the same payload objects.
+try:
+    from gact import _hooks
+    _hooks.bind(Packed)
+except ImportError:
+    _hooks = None
+
+
+def launches():
+    """Library kernels enqueued so far by this module and by the native hooks."""
+    return launch_count + (_hooks.launches() if _hooks is not None else 0)
+
+
 _dense_cache = {}
 
 
@@ -237,7 +260,7 @@ def quantize_compact(input, q_bit, seed):
     strides = None
     if input.is_contiguous():
         x = input
-    elif config.keep_layout and (input.data_ptr() & 15) == 0 and _is_dense_permutation(tuple(input.shape), input.stride()):
+    elif config.keep_layout and _is_dense_permutation(tuple(input.shape), input.stride()):
         x, strides = input, input.stride()
     else:
         x = input.contiguous()

@@ -12,6 +12,7 @@ import torch
 from gact.conf import config
 from gact.ops import op_quantize, op_dequantize, op_quantize_mask, op_dequantize_mask
 from gact import ops as _ops
+from gact.ops import _hooks
 from gact.utils import uniform_sample
 
 
@@ -38,6 +39,7 @@ class Quantizer:
             self.end_prefetch_event = torch.cuda.Event(blocking=True)
         self.layer_key_map = {}
         self.tid = 0
+        self.tids_registered = 0    # tids handed out during iteration 0, shared payloads included
         self.start_bwd = True
         # collected for auto precision
         self.seeds = {}
@@ -125,6 +127,12 @@ class Quantizer:
         return True, True, q_inputs
 
     def quantize(self, input):
+        # The plain case (a floating-point activation, no swapping, no value fingerprints) is handled by the native
+        # module when it is there; it answers NotImplemented, before changing anything, for everything else.
+        if _hooks is not None and config.native_hooks:
+            r = _hooks.quantize(self, config, input)
+            if r is not NotImplemented:
+                return r
         # Same decisions as check_quantize, cheapest tests first: this runs for every saved tensor of every step.
         dt = input.dtype
         if dt is torch.float32 or dt is torch.float16 or (dt is torch.bfloat16 and config.quantize_bf16):
@@ -141,6 +149,8 @@ class Quantizer:
 
         tid = self.tid
         self.tid += 1
+        if self.iter == 0:
+            self.tids_registered = self.tid
         input_shape = input.shape
 
         # The same tensor object saved again, unmodified (e.g. one activation feeding three linear layers): share
@@ -162,8 +172,15 @@ class Quantizer:
                 self.dims[tid] = input.numel()
                 self.seeds[tid] = tid
             else:
-                bit = self.bits[tid]
-            seed = self.seeds[tid] + self.seed_iter + self.seed_offset
+                bit = self.bits.get(tid)
+                if bit is None:
+                    # A tid that shared another save's payload while the widths were registered (iteration 0) has
+                    # no entry of its own; should a later step save it on its own after all, it takes the default
+                    # width.  A tid iteration 0 never saw is an error, as in the reference (static graph).
+                    if tid >= self.tids_registered:
+                        raise KeyError(tid)
+                    bit = self.default_bit
+            seed = self.seeds.get(tid, tid) + self.seed_iter + self.seed_offset
             if bit == 32:
                 q_inputs = op_quantize(input, bit, seed)
             else:
@@ -198,6 +215,10 @@ class Quantizer:
         self._set_payload(q_inputs, q_cpu)
 
     def dequantize(self, input):
+        if _hooks is not None and config.native_hooks:
+            r = _hooks.dequantize(self, input)
+            if r is not NotImplemented:
+                return r
         quantized = input[0]
         if not quantized:
             return input[1]

@@ -6,7 +6,10 @@ workload follows the loop of the reference drivers: forward / backward / optimiz
 ``controller.iterate(backprop)`` where ``backprop`` runs one forward + backward on the first 8 samples
 (reference: benchmark/text_classification/run_glue.py:611-623, benchmark/vision/train.py:316-330).
 
-    build(name, device, batch, dtype_autocast) -> Workload(model, step(), backprop(), samples_per_step)
+    BUILDERS[name](device, batch=..., world=..., seed=...) -> Workload(model, step(), backprop(), forward(), finish(), ...)
+
+``activation_memory`` and ``batch_ladder`` measure what the reference's drivers report with ``--get-mem`` and what
+its ``exp_mem_speed.py`` sweeps search for (activation bytes per step, largest batch that fits).
 """
 from __future__ import annotations
 
@@ -28,6 +31,8 @@ class Workload:
     backprop: Callable[[], None]            # forward + backward on the probe batch (first 8 samples)
     samples_per_step: int
     describe: dict
+    forward: Callable[[], tuple] = None      # forward pass on the full batch -> (loss, [outputs])
+    finish: Callable[[torch.Tensor], None] = None   # backward + optimizer step for that loss
 
 
 DDP_BUCKET_MB = 25          # torch's default; benchmarks may raise it (fewer, larger NVLink all-reduces)
@@ -56,25 +61,32 @@ def bert_large(device, batch=64, seq_len=128, world=1, seed=0, layers=24, autoca
     labels = torch.randint(0, 2, (batch,), device=device, generator=g)
     mask = torch.ones_like(ids)
 
-    def fwd_bwd(i, m, y):
+    def fwd(i, m, y):
         with torch.autocast("cuda", dtype=autocast, enabled=autocast is not None):
             out = model(input_ids=i, attention_mask=m, labels=y)
-        out.loss.backward()
-        return out.loss
+        return out.loss, [out.logits]
+
+    def forward():
+        opt.zero_grad(set_to_none=True)
+        return fwd(ids, mask, labels)
+
+    def finish(loss):
+        loss.backward()
+        opt.step()
 
     def step():
-        opt.zero_grad(set_to_none=True)
-        loss = fwd_bwd(ids, mask, labels)
-        opt.step()
+        loss, _ = forward()
+        finish(loss)
         return loss.detach()
 
     def backprop():
         opt.zero_grad(set_to_none=True)
-        fwd_bwd(ids[:8], mask[:8], labels[:8])
+        fwd(ids[:8], mask[:8], labels[:8])[0].backward()
 
     return Workload("bert_large", model, opt, step, backprop, batch,
                     {"model": "BERT-large seq-cls (random init)", "layers": layers, "seq_len": seq_len, "batch_per_gpu": batch,
-                     "optimizer": "AdamW lr 2e-5", "autocast": str(autocast).split(".")[-1] if autocast else "off"})
+                     "optimizer": "AdamW lr 2e-5", "autocast": str(autocast).split(".")[-1] if autocast else "off"},
+                    forward, finish)
 
 
 def resnet50(device, batch=256, world=1, seed=0, autocast=None) -> Workload:
@@ -89,24 +101,33 @@ def resnet50(device, batch=256, world=1, seed=0, autocast=None) -> Workload:
     x = torch.randn(batch, 3, 224, 224, device=device, generator=g)
     y = torch.randint(0, 1000, (batch,), device=device, generator=g)
 
-    def fwd_bwd(a, b):
+    def fwd(a, b):
         with torch.autocast("cuda", dtype=autocast, enabled=autocast is not None):
-            loss = F.cross_entropy(model(a), b)
+            out = model(a)
+            loss = F.cross_entropy(out, b)
+        return loss, [out]
+
+    def forward():
+        opt.zero_grad(set_to_none=True)
+        return fwd(x, y)
+
+    def finish(loss):
         loss.backward()
-        return loss
+        opt.step()
 
     def step():
-        opt.zero_grad(set_to_none=True)
-        loss = fwd_bwd(x, y)
-        opt.step()
+        loss, _ = forward()
+        finish(loss)
         return loss.detach()
 
     def backprop():
         opt.zero_grad(set_to_none=True)
-        fwd_bwd(x[:8], y[:8])
+        fwd(x[:8], y[:8])[0].backward()
 
     return Workload("resnet50", model, opt, step, backprop, batch,
-                    {"model": "ResNet-50 (random init)", "batch_per_gpu": batch, "optimizer": "SGD momentum 0.9"})
+                    {"model": "ResNet-50 (random init)", "batch_per_gpu": batch, "optimizer": "SGD momentum 0.9",
+                     "autocast": str(autocast).split(".")[-1] if autocast else "off"},
+                    forward, finish)
 
 
 class GCN(nn.Module):
@@ -166,24 +187,92 @@ def gcn(device, world=1, seed=0, nodes=169343, feat=128, hidden=256, classes=40,
     model.train()
     opt = torch.optim.Adam(model.parameters(), lr=0.01)
 
-    def fwd_bwd():
-        loss = F.cross_entropy(model(adj, x), y)
+    def forward():
+        opt.zero_grad(set_to_none=True)
+        out = model(adj, x)
+        return F.cross_entropy(out, y), [out]
+
+    def finish(loss):
         loss.backward()
-        return loss
+        opt.step()
 
     def step():
-        opt.zero_grad(set_to_none=True)
-        loss = fwd_bwd()
-        opt.step()
+        loss, _ = forward()
+        finish(loss)
         return loss.detach()
 
     def backprop():
         opt.zero_grad(set_to_none=True)
-        fwd_bwd()
+        forward()[0].backward()
 
     return Workload("gcn", model, opt, step, backprop, 1,
                     {"model": "3-layer GCN, hidden 256", "nodes": nodes, "undirected_edges": int((e.shape[1] - nodes) // 2),
-                     "optimizer": "Adam lr 0.01", "unit_note": "one sample = one full-batch epoch"})
+                     "optimizer": "Adam lr 0.01", "unit_note": "one sample = one full-batch epoch"},
+                    forward, finish)
 
 
 BUILDERS = {"bert_large": bert_large, "resnet50": resnet50, "gcn": gcn}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Memory, measured the way the reference's drivers do with --get-mem (benchmark/vision/train.py:242-281,
+# benchmark/text_classification/run_glue.py:508-559): allocated bytes right before backward, minus the level before
+# the forward pass (weights, optimizer state, data, gradients of the previous step) and minus loss and outputs, is
+# what the saved tensors of one step hold.
+# ---------------------------------------------------------------------------------------------------------------
+def _nbytes(ts):
+    return sum(t.numel() * t.element_size() for t in ts)
+
+
+def activation_memory(wl: Workload, iterate: Callable[[], None] = None) -> dict:
+    """One training step with the three readings of the reference protocol.  ``iterate``: what follows the optimizer
+    step in the training loop (``controller.iterate(backprop)``), or None."""
+    torch.cuda.synchronize()
+    init = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    loss, outs = wl.forward()
+    torch.cuda.synchronize()
+    before_backward = torch.cuda.memory_allocated()
+    act = before_backward - init - _nbytes([loss] + list(outs))
+    del outs
+    wl.finish(loss)
+    del loss
+    if iterate is not None:
+        iterate()
+    torch.cuda.synchronize()
+    after = torch.cuda.memory_allocated()
+    return {"activation_bytes": int(act), "before_forward_bytes": int(init), "before_backward_bytes": int(before_backward),
+            "after_step_bytes": int(after), "peak_bytes": int(torch.cuda.max_memory_allocated())}
+
+
+def batch_ladder(build: Callable[[int], tuple], start: int, limit_bytes: int, max_rungs: int = 12) -> list:
+    """Doubles the batch while the NEXT rung is predicted to stay below ``limit_bytes`` (a linear fit of the peak over
+    the rungs measured so far), instead of the reference's search by running out of memory
+    (benchmark/vision/exp_mem_speed.py:42-54).  ``build(batch)`` -> (workload, iterate or None, cleanup); every rung
+    runs two steps and reports the second.  Returns one record per rung; the last carries ``predicted_max_batch``."""
+    rungs = []
+    b = start
+    for _ in range(max_rungs):
+        wl, iterate, cleanup = build(b)
+        try:
+            wl.step()
+            if iterate is not None:
+                iterate()
+            m = activation_memory(wl, iterate)
+        finally:
+            cleanup()
+            del wl
+            torch.cuda.empty_cache()
+        m["batch"] = b
+        rungs.append(m)
+        if len(rungs) >= 2:
+            (b0, p0), (b1, p1) = [(r["batch"], r["peak_bytes"]) for r in rungs[-2:]]
+            slope = max((p1 - p0) / (b1 - b0), 1.0)
+        else:
+            slope = max((m["activation_bytes"] * 1.3) / b, 1.0)          # first guess: activations dominate the growth
+        fixed = m["peak_bytes"] - slope * b
+        m["predicted_max_batch"] = int((limit_bytes - fixed) // slope)
+        if fixed + slope * 2 * b > limit_bytes:
+            break
+        b *= 2
+    return rungs

@@ -5,8 +5,14 @@
  * (0 = GACT_OK, see gact_error_string) and never throws.  The caller owns every buffer.  Kernels are
  * enqueued on the stream passed in (a cudaStream_t, 0 = the legacy default stream) of the CURRENT device;
  * nothing synchronises with the host and nothing is allocated unless a comment says otherwise.
- * The library keeps no mutable global state (the one exception is documented at gact_sq_diffs3_noalloc), so
- * calls may come from any thread (PyTorch runs the backward-side calls on its autograd worker threads).
+ * Calls may come from any thread (PyTorch runs the backward-side calls on its autograd worker threads).
+ * Process-wide state the library does keep, all of it safe to touch from several threads:
+ *   - per-device caches filled on first use: the SM count, each kernel's resident-block count and
+ *     shared-memory opt-in, the device address of the gact_sq_diffs3_noalloc scratch array (none of them
+ *     survives cudaDeviceReset: do not reset a device the library has been used on and then go on using it);
+ *   - the sticky error word of the bulk-copy pipeline (gact_pipeline_error / gact_pipeline_error_reset);
+ *   - the diagnostics knobs of gact_pipeline_test_hook;
+ *   - the scratch array of gact_sq_diffs3_noalloc (documented there).
  *
  * Each declaration names the interface of the reference implementation (paths inside the GACT
  * repository) that it replaces.
@@ -63,7 +69,10 @@ int64_t gact_packed_bytes(int64_t n, int bits);
  * Replaces minimax() (gact/gact/cpp_extension/minimax.cc:7-10, minimax_cuda_kernel.cu:23-89) followed by
  * pack_single_precision() (gact/gact/cpp_extension/quantization.cc:51-61,
  * quantization_cuda_kernel.cu:23-146) as called from gact/gact/ops.py:11-32.
- *   x       n elements of `dtype`, 16-byte aligned
+ *   x       n elements of `dtype`, aligned to the element size.  Any contiguous tensor is accepted, as by the
+ *           reference (gact/gact/cpp_extension/ext_common.h:2-27); 16-byte alignment (what an allocator returns)
+ *           selects the vectorised loads, anything else - a contiguous view that starts at an odd offset of its
+ *           storage - is read element by element, same result, several times slower
  *   packed  R*256 bytes (gact_packed_bytes), 16-byte aligned
  *   qmin    G elements of `dtype`
  *   qscale  G elements of `dtype`; for GACT_BF16 (a type the reference does not compress) G floats: bf16
@@ -77,26 +86,33 @@ int gact_quantize(const void* x, int dtype, int64_t n, int bits, uint64_t seed, 
                   const float* noise, int fma_mode, void* packed, void* qmin, void* qscale, void* stream);
 
 /*
- * 0 while every bounded wait inside the bulk-copy pipeline of gact_quantize has been satisfied; non-zero once a
- * wait ran out (the kernel then winds down instead of spinning).  Synchronises with the device; for tests and
- * diagnostics.  -1 if the value could not be read.
+ * The fp16 / bf16 kernel of gact_quantize stages its input through shared memory with bulk copies and waits for
+ * them on mbarriers.  Every such wait is bounded; a wait that runs out makes the warp record an error and leave
+ * (the tiles it had not written keep whatever the output buffers held), so a launch can never spin forever.
+ * gact_pipeline_error: 0 while no wait has ever run out on the current device, non-zero afterwards (sticky);
+ * -1 if the word could not be read.  gact_pipeline_error_reset: clears it.  Both synchronise with the device,
+ * so call them where the host waits anyway (the Python layer does so once per adaptation and when the hooks
+ * are removed, and raises).  No counterpart in the reference, whose kernels never wait.
  */
 int gact_pipeline_error(void);
+int gact_pipeline_error_reset(void);
 
 /*
- * Tuning knob without a reference counterpart: gact_quantize runs 16-bit inputs with generated noise through
- * its bulk-copy ring kernel when the tensor holds at least `min_chunks` whole 32 KB chunks (default 1536, i.e.
- * 48 MB), and through the direct-load kernel otherwise; both give the same bytes.  Returns the previous value;
- * min_chunks < 1 only reads it.  Process-wide; tests lower it to push small cases through the ring.
+ * Diagnostics, no counterpart in the reference.  wait_limit: polls after which a wait of the pipeline above gives
+ * up (0 restores the default, 2^20).  withhold_one_copy != 0: warp 0 of block 0 leaves its first bulk copy
+ * unissued, so that its wait runs out after wait_limit polls - the only way to see the give-up path work without
+ * a broken GPU.  Process-wide, read at launch; meant for the test-suite.
  */
-int64_t gact_set_ring_min_chunks(int64_t min_chunks);
+void gact_pipeline_test_hook(uint32_t wait_limit, int withhold_one_copy);
 
 /*
  * Unpack + dequantize: out[i] = T(T(code)/scale) + min for the first n elements (bf16, not a reference type:
  * bf16(fma(code, fl32(1/scale), min)) with the fp32 qscale written by gact_quantize).
  * Replaces unpack_single_precision() (gact/gact/cpp_extension/quantization.cc:36-49,
  * quantization_cuda_kernel.cu:149-221) and the slice in gact/gact/ops.py:61-69.
- *   out     n elements of `dtype`, 16-byte aligned (no padded tail is written)
+ *   out     n elements of `dtype`, aligned to the element size (16-byte alignment selects vector stores);
+ *           no padded tail is written
+ *   packed  16-byte aligned
  */
 int gact_dequantize(const void* packed, const void* qmin, const void* qscale, int dtype, int64_t n,
                     int bits, void* out, void* stream);
@@ -111,7 +127,7 @@ int gact_minimax(const void* x, int dtype, int64_t n, void* mn, void* mx, void* 
  * 1-bit packing of a 0/1 byte tensor (uint8 or bool dropout mask): element e goes to bit (t/16) of word
  * (e/512)*16 + t%16, t = e%512.  words: gact_mask_words(n) = ceil(n/512)*16 uint32 (a partial last block
  * still uses all of its 16 words; the reference allocates ceil(n/32) and runs past it), 4-byte aligned;
- * x: 16-byte aligned.
+ * x: any address (16-byte alignment selects vector loads).
  * Replaces act_quantize_dropout_mask() (gact/gact/cpp_extension/quantization.cc:26-29,
  * quantization_cuda_kernel.cu:229-274), without its out-of-bounds tail write.
  * not_binary (optional device int, caller zeroes it): set to 1 when some byte is neither 0 nor 1; this
@@ -154,12 +170,18 @@ int gact_sq_diffs3(const float* g0, const float* g1, const float* g2, int64_t P,
  * cudaMalloc / cudaFree and no allocating library routine.
  *
  * Differences from gact_sq_diffs3: no `scratch` argument; the three segment tables are HOST arrays
- * (seg_ptr_host[k] is still a device pointer), copied by the call itself, in stream order, into the library's
- * table, so they may be reused as soon as the call returns.  Limit: nseg <= GACT_NOALLOC_MAX_SEGMENTS, else
+ * (seg_ptr_host[k] is still a device pointer), copied by the call itself, in stream order (cudaMemcpyAsync),
+ * into the library's table.  Tables in PAGEABLE host memory are staged by the runtime before the call returns
+ * and may be reused at once; tables in PINNED host memory are read by the copy engine when the stream gets
+ * there, so keep them unchanged until then (an event after the call, or any later synchronisation of the
+ * stream).  Because the tables are on the host they are checked before anything is launched: the segments must
+ * tile [0, P) in order (seg_off_host[0] = 0, each offset = the previous offset + length, lengths summing to P,
+ * no null pointer), else GACT_ERR_SIZE / GACT_ERR_NULL.  Limit: nseg <= GACT_NOALLOC_MAX_SEGMENTS, else
  * GACT_ERR_NOALLOC_LIMIT and nothing is launched; P is not limited.  nseg = 0 selects the contiguous g2.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
- * current) and caches it; make that first call outside of any stream capture.  All calls on a device share the
+ * current) and caches it; make that first call outside of any stream capture.  The cached address belongs to the
+ * device's current context: it does not survive cudaDeviceReset.  All calls on a device share the
  * one array, which simply keeps what the last call left in it; nothing in it has to start at zero, because
  * every call rewrites the partials and the table entries it reads before reading them.  For the same reason
  * two calls that overlap on the GPU (different streams, or different threads on different streams) race on it:

@@ -16,8 +16,17 @@ GROUP = 256
 
 
 class FakeLib:
+    pipeline_error = 0          # tests set this to see the Python layer react
+
     def gact_version(self):
         return 100
+
+    def gact_pipeline_error(self):
+        return self.pipeline_error
+
+    def gact_pipeline_error_reset(self):
+        FakeLib.pipeline_error = 0
+        return 0
 
     def gact_error_string(self, st):
         return b"fake"
@@ -92,6 +101,14 @@ class FakeNative:
         if status:
             raise RuntimeError(f"{what}: status {status}")
 
+    GactError = RuntimeError
+
+    @staticmethod
+    def check_pipeline(where):
+        if FakeNative.lib.gact_pipeline_error() > 0:
+            FakeNative.lib.gact_pipeline_error_reset()
+            raise RuntimeError(f"{where}: pipeline error")
+
     @staticmethod
     def require_cuda(t, name):
         return None
@@ -116,4 +133,7 @@ def install(monkeypatch):
     import gact.quantizer
     monkeypatch.setattr(gact.ops, "nv", FakeNative)
     monkeypatch.setattr(gact.autoprec, "nv", FakeNative)
+    import gact.controller
+    monkeypatch.setattr(gact.controller, "_nv", FakeNative)
+    monkeypatch.setattr(gact.quantizer, "_hooks", None)        # the native hooks only take CUDA tensors
     monkeypatch.setattr(gact.quantizer.Quantizer, "_on_device", staticmethod(lambda t: True))

@@ -17,7 +17,8 @@ def declared_functions():
 def test_header_declares_the_expected_entry_points():
     names = declared_functions()
     for must in ("gact_quantize", "gact_dequantize", "gact_minimax", "gact_mask_pack", "gact_mask_unpack", "gact_sq_diffs3",
-                 "gact_sensitivity", "gact_calc_precision", "gact_packed_bytes", "gact_mask_words", "gact_error_string", "gact_version"):
+                 "gact_sensitivity", "gact_calc_precision", "gact_packed_bytes", "gact_mask_words", "gact_error_string", "gact_version",
+                 "gact_pipeline_error", "gact_pipeline_error_reset", "gact_pipeline_test_hook", "gact_sq_diffs3_noalloc"):
         assert must in names
 
 
@@ -53,7 +54,8 @@ def test_argument_validation_without_a_gpu():
     assert f(p, 0, 512, 3, 0, 0, None, 1, p, p, p, None) == 1            # bits
     assert f(p, 9, 512, 2, 0, 0, None, 1, p, p, p, None) == 2            # dtype
     assert f(None, 0, 512, 2, 0, 0, None, 1, p, p, p, None) == 3         # null pointer
-    assert f(p + 4, 0, 100, 2, 0, 0, None, 1, p, p, p, None) == 4        # alignment
+    assert f(p + 2, 0, 100, 2, 0, 0, None, 1, p, p, p, None) == 4        # x not aligned to its element size
+    assert f(p, 0, 100, 2, 0, 0, None, 1, p + 8, p, p, None) == 4        # packed output not 16-byte aligned
     assert f(p, 0, -1, 2, 0, 0, None, 1, p, p, p, None) == 5             # size
     assert f(p, 0, 512, 2, 0, 7, None, 1, p, p, p, None) == 6            # rng mode
     assert f(p, 0, 512, 2, 0, 3, None, 1, p, p, p, None) == 6            # external noise missing
@@ -63,6 +65,20 @@ def test_argument_validation_without_a_gpu():
     assert nv.lib.gact_calc_precision(None, None, None, 0, 1.0, None, None) == 0
     assert nv.lib.gact_calc_precision(None, None, None, 5, 1.0, None, None) == 3
     assert nv.lib.gact_sq_diffs3_noalloc(p, p, None, 8, p, p, p, 5000, p, None) == 9      # more segments than it holds
+    # the host tables of the allocation-free entry point are checked before anything is launched
+    h = nv.lib.gact_sq_diffs3_noalloc
+    ptrs = (ctypes.c_uint64 * 3)(p, p, p)
+    lens = (ctypes.c_int64 * 3)(4, 2, 2)
+
+    def tables(offs, lens_=lens, ptrs_=ptrs):
+        o = (ctypes.c_int64 * 3)(*offs)
+        return h(p, p, None, 8, ctypes.addressof(ptrs_), ctypes.addressof(o), ctypes.addressof(lens_), 3, p, None)
+
+    assert tables([1, 5, 7]) == 5                                       # does not start at 0
+    assert tables([0, 5, 7]) == 5                                       # a gap
+    assert tables([0, 3, 5]) == 5                                       # overlap
+    assert tables([0, 4, 6], lens_=(ctypes.c_int64 * 3)(4, 2, 1)) == 5  # lengths do not add up to P
+    assert tables([0, 4, 6], ptrs_=(ctypes.c_uint64 * 3)(p, 0, p)) == 3  # a null segment
 
 
 def test_import_fails_loudly_without_the_library(tmp_path, monkeypatch):

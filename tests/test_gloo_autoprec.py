@@ -36,6 +36,9 @@ def _worker(rank, world, port, mode, out_dir):
     gact.ops.nv = fake_native.FakeNative
     gact.autoprec.nv = fake_native.FakeNative
     gact.quantizer.Quantizer._on_device = staticmethod(lambda t: True)
+    gact.quantizer._hooks = None                           # the native hooks only take CUDA tensors
+    import gact.controller
+    gact.controller._nv = fake_native.FakeNative
     gact.config.reset()
     gact.set_optimization_level("L2")
     gact.config.dp_probe = mode

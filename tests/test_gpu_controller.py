@@ -304,3 +304,51 @@ def test_training_converges_like_the_uncompressed_run(rng_mode):
     comp = train("L1.2")                                       # fixed 2 bits on every saved tensor
     assert base[-1] < base[0] - 0.3                            # measured: 2.315 -> 1.80
     np.testing.assert_allclose(comp, base, atol=0.05, rtol=0)  # measured: the curves differ by less than 0.01
+
+
+def test_saved_views_at_odd_offsets_are_compressed():
+    """A contiguous view that does not start on a 16-byte boundary (t[1:] of a tensor with an odd row length) is
+    compressed like any other tensor - the reference accepts every contiguous CUDA tensor
+    (gact/gact/cpp_extension/ext_common.h:2-27) - both through the op and through the hooks."""
+    import gact
+    from gact.ops import op_quantize, op_dequantize, op_quantize_mask, op_dequantize_mask
+    h = torch.randn(5, 33, 7).half()
+    v = h.cuda()[1:]
+    assert v.is_contiguous() and v.data_ptr() % 16 != 0
+    for mode in ("fast", "curand"):
+        gact.config.rng_mode = mode
+        q = op_quantize(v, 4, 3)
+        oq = oracle.op_quantize(h[1:].contiguous(), 4, 3, rng_mode=mode)
+        assert torch.equal(q[0].cpu()[:-1], oq[0][:-1])
+        assert_bits_equal(q[2], oq[2], "scale")
+        assert_bits_equal(q[3], oq[3], "min")
+        assert_bits_equal(op_dequantize(q, v.shape), oracle.op_dequantize(oq, v.shape), "dequantized")
+    m = (torch.rand(5, 33, 7, device="cuda") < 0.5)[1:]
+    assert m.data_ptr() % 16 != 0
+    assert torch.equal(op_dequantize_mask(op_quantize_mask(m), dtype=torch.bool), m)
+
+    gact.config.reset()
+    gact.set_optimization_level("L1.1")           # fixed 8 bits
+    w = torch.randn(33, 7, device="cuda")
+
+    def run(hooked):
+        base = torch.randn(5, 33, 7, device="cuda", generator=torch.Generator(device="cuda").manual_seed(0)).requires_grad_()
+        ctl = gact.Controller(nn.Linear(1, 1).cuda()) if hooked else None
+        if hooked:
+            ctl.install_hook()
+        try:
+            view = base[1:]                        # saved by the multiplication below, at an odd offset
+            assert view.data_ptr() % 16 != 0
+            ((view * view) * w).sum().backward()
+            n = len(ctl.quantizer.bits) if hooked else 0
+        finally:
+            if hooked:
+                ctl.uninstall_hook()
+        return base.grad, n
+
+    exact, _ = run(False)
+    got, compressed = run(True)
+    assert compressed >= 1
+    # 8-bit codes: the saved values are off by up to one step (range / 255 ~ 0.03), the gradient 2 * v * w by |2 w| times that
+    torch.testing.assert_close(got, exact, rtol=0.05, atol=0.3)
+    assert float((got - exact).abs().mean()) < 0.03

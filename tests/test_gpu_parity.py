@@ -13,14 +13,11 @@ pytestmark = pytest.mark.gpu
 
 
 
-@pytest.fixture(autouse=True, params=["ring", "default"])
-def ring_threshold(request):
-    """Every test of this module runs twice: with the ring kernel taking every tensor of at least one 32 KB chunk,
-    and with the library's own choice (ring from 48 MB on, direct loads below)."""
+@pytest.fixture(autouse=True)
+def no_wait_ran_out():
+    """The fp16 / bf16 kernel waits for its bulk copies with a bound; none of these tests may ever hit it."""
     from gact import _native as nv
-    before = nv.lib.gact_set_ring_min_chunks(1 if request.param == "ring" else 0)
-    yield request.param
-    nv.lib.gact_set_ring_min_chunks(before)
+    yield
     assert nv.lib.gact_pipeline_error() == 0
 
 
@@ -174,18 +171,17 @@ def test_argument_errors():
     assert f(x.data_ptr(), 0, 512, 3, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 1      # bits
     assert f(x.data_ptr(), 7, 512, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 2      # dtype
     assert f(None, 0, 512, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 3              # null
-    assert f(x.data_ptr() + 4, 0, 500, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 4  # alignment
+    assert f(x.data_ptr() + 2, 0, 500, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 4  # not even element-aligned
+    assert f(x.data_ptr(), 0, 512, 2, 0, 0, None, 1, pk.data_ptr() + 8, q.data_ptr(), q.data_ptr(), s) == 4  # packed output
     assert f(x.data_ptr(), 0, -1, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 5       # size
     assert f(x.data_ptr(), 0, 512, 2, 0, 3, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 6      # noise missing
     assert f(x.data_ptr(), 0, 0, 2, 0, 0, None, 1, pk.data_ptr(), q.data_ptr(), q.data_ptr(), s) == 0        # empty input
     torch.cuda.synchronize()
 
 
-def test_more_than_2_to_31_elements(ring_threshold):
+def test_more_than_2_to_31_elements():
     """64-bit indexing: a 4.3 GB fp16 tensor; the far end is checked against the oracle (round to nearest has no
     index-dependent noise, so a slice that starts on a row-block boundary can be checked on its own)."""
-    if ring_threshold == "ring":
-        pytest.skip("round to nearest never takes the ring kernel")
     from gact.ops import quantize_pack, dequantize_and_unpack
     n = (1 << 31) + 256 * 12 + 100
     free, _ = torch.cuda.mem_get_info()
@@ -213,14 +209,119 @@ def test_more_than_2_to_31_elements(ring_threshold):
     torch.cuda.empty_cache()
 
 
+# ---- the sizes at which the 16-bit kernel changes what it does ------------------------------------------------------
+TILE = 8 * 256                      # elements per warp tile
+WARPS = 148 * 3 * 8                 # resident warps of a full launch on a B200
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("bits", BITS)
-def test_above_the_ring_threshold(dtype, bits, ring_threshold):
-    """50 MB tensors: the size from which the library picks the ring kernel by itself, plus a ragged tail."""
-    if ring_threshold == "ring":
-        pytest.skip("same kernel either way at this size")
-    n = 1536 * 16384 + 3 * 16384 + 1000
-    x = make_input("relu", n, dtype, seed=bits)
-    check_case(x, bits, 5, "fast")
-    if bits in (2, 8):
-        check_case(x, bits, 5, "curand")
+def test_tile_and_wave_boundaries(dtype, bits):
+    """Whole tiles only / one group more / a ragged end; fewer tiles than a block has warps; one tile fewer, as many
+    and one more than the resident warps (where a warp's second stage comes into use), and twice that plus one
+    (where the first stage is refilled)."""
+    sizes = [TILE, TILE + 256, TILE - 1, 3 * TILE + 5 * 256 + 77, 8 * TILE, 9 * TILE + 1,
+             (WARPS - 1) * TILE, WARPS * TILE + 100, (WARPS + 1) * TILE + 256 * 3, (2 * WARPS + 1) * TILE + 19]
+    for j, n in enumerate(sizes):
+        check_case(make_input("relu" if j % 2 else "randn", n, dtype, seed=j), bits, 3 + j, "fast")
+    check_case(make_input("randn", (2 * WARPS + 1) * TILE + 19, dtype, seed=5), bits, 1, "rtn")
+    if bits in (1, 4):
+        check_case(make_input("special", (WARPS + 2) * TILE + 300, dtype, seed=6), bits, 2, "curand")
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_mixed_list_sizes(bits):
+    """2^20 ... 2^26 elements, the sizes of the sweep's mixed list."""
+    for k in range(20, 27):
+        check_case(make_input("randn", 1 << k, torch.float16, seed=k), bits, k, "fast")
+
+
+# ---- the whole benchmark tensor --------------------------------------------------------------------------------------
+_BIG = {}
+
+
+def big_relu(dtype):
+    if dtype not in _BIG:
+        g = torch.Generator().manual_seed(0)
+        _BIG[dtype] = torch.randn(128 * 64 * 112 * 112, generator=g).clamp_min_(0).to(dtype)
+    return _BIG[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", BITS)
+def test_whole_config2_tensor(dtype, bits):
+    """128x64x112x112 post-ReLU activations: every packed byte, min, scale and dequantized value of the full tensor
+    against the oracle - the default mode for both types, the reference's stream for fp16 (the reference has no bf16)."""
+    x = big_relu(dtype)
+    check_case(x, bits, 42, "fast")
+    if dtype == torch.float16:
+        check_case(x, bits, 42, "curand")
+    if bits == 2:
+        check_case(x, bits, 42, "rtn")
+
+
+# ---- contiguous tensors that do not start on a 16-byte boundary ----------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bits", [1, 4])
+def test_inputs_at_odd_offsets(dtype, bits):
+    """A contiguous view may start anywhere in its storage (t[1:] of a tensor with an odd row length); the reference
+    takes any contiguous tensor.  Same bytes as for an aligned copy, and the output may sit at an odd offset too."""
+    from gact import _native as nv
+    for off, n in ((1, 256 * 21 + 3), (3, 5 * TILE + 77), (5, 300)):
+        base = make_input("randn", n + off, dtype, seed=off)
+        x_cpu = base[off:].clone()
+        xg = base.cuda()[off:]
+        assert xg.data_ptr() % 16 != 0 and xg.is_contiguous()
+        for mode in ("fast", "curand", "rtn"):
+            pk, mn, sc = abi_quantize(xg, bits, 9, mode)
+            opk, omn, osc = oracle.quantize(x_cpu, bits, 9, mode)
+            assert_bits_equal(pk, opk, "packed")
+            assert_bits_equal(mn, omn, "min")
+            assert_bits_equal(sc, osc, "scale")
+        # dequantize into a view at an odd offset, with guard elements on both sides
+        out = torch.full((n + off + 8,), -777.0, dtype=dtype, device="cuda")
+        view = out[off:off + n]
+        st = nv.lib.gact_dequantize(opk.cuda().data_ptr(), omn.cuda().data_ptr(), osc.cuda().data_ptr(), nv.DTYPE_CODE[dtype],
+                                    n, bits, view.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        torch.cuda.synchronize()
+        assert_bits_equal(view, oracle.dequantize(opk, omn, osc, n, bits), "dequantized")
+        assert bool((out[:off] == -777.0).all()) and bool((out[off + n:] == -777.0).all())
+        # min / max only
+        G = (n + 255) // 256
+        lo = torch.empty(G, dtype=dtype, device="cuda")
+        hi = torch.empty(G, dtype=dtype, device="cuda")
+        assert nv.lib.gact_minimax(xg.data_ptr(), nv.DTYPE_CODE[dtype], n, lo.data_ptr(), hi.data_ptr(),
+                                   torch.cuda.current_stream().cuda_stream) == 0
+        wlo, whi = oracle.minimax(x_cpu)
+        assert_bits_equal(lo, wlo, "min")
+        assert_bits_equal(hi, whi, "max")
+
+
+# ---- a wait of the bulk-copy pipeline that runs out ------------------------------------------------------------------
+def test_bounded_wait_runs_out_and_the_library_recovers():
+    """With one bulk copy withheld (a diagnostics switch) the waiting warp gives up after the wait limit, records the
+    error and leaves; the launch ends by itself.  After a reset the next launch is bit-exact again.  Nothing faults
+    and nothing spins: the wait is a bounded poll of an mbarrier that simply never completes."""
+    from gact import _native as nv
+    x_cpu = make_input("randn", 64 * TILE + 100, torch.float16, seed=1)
+    x = x_cpu.cuda()
+    assert nv.lib.gact_pipeline_error() == 0
+    nv.lib.gact_pipeline_test_hook(2000, 1)
+    try:
+        n = x.numel()
+        pk = torch.zeros(nv.lib.gact_packed_bytes(n, 4), dtype=torch.uint8, device="cuda")
+        mn = torch.zeros((n + 255) // 256, dtype=torch.float16, device="cuda")
+        sc = torch.zeros_like(mn)
+        st = nv.lib.gact_quantize(x.data_ptr(), nv.F16, n, 4, 1, nv.RNG_FAST, None, 1, pk.data_ptr(), mn.data_ptr(), sc.data_ptr(),
+                                  torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        torch.cuda.synchronize()                                   # the launch finished on its own
+        assert nv.lib.gact_pipeline_error() == 2
+        with pytest.raises(nv.GactError):
+            nv.check_pipeline("test")                              # what the Python layer does at its sync points
+    finally:
+        nv.lib.gact_pipeline_test_hook(0, 0)
+        nv.lib.gact_pipeline_error_reset()
+    assert nv.lib.gact_pipeline_error() == 0
+    check_case(x_cpu, 4, 1, "fast")

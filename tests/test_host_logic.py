@@ -310,3 +310,118 @@ def test_dense_permuted_views_are_compressed_in_memory_order(fake):
     config.keep_layout = False
     r = q.quantize(x)
     assert q.ptr_qtensor_map[r[2]][0].strides is None
+
+
+def test_logging_and_debug_branches(fake, tmp_path, capsys):
+    """log_interval > 0 and debug = True (reference: gact/gact/autoprec.py:131-183,211-234): autoprec.log gets one
+    JSON record per logged iteration, the variance comparison is printed, and the too-large-variance warning is
+    recorded when the quantization variance exceeds a tenth of the gradient variance."""
+    import json
+    config.reset()
+    gact.set_optimization_level("L2")
+    gact.set_adapt_interval(2)
+    config.log_interval = 1
+    config.debug = True
+    config.work_dir = str(tmp_path) + "/"
+    torch.manual_seed(0)
+    model = TinyNet()
+    x, y = torch.randn(32, 64), torch.randint(0, 8, (32,))
+    ctl = Controller(model)
+    ctl.ap.warmpup_iter = 0                      # the reference only warns after 100 iterations
+    ctl.install_hook()
+
+    def backprop():
+        model.zero_grad()
+        F.cross_entropy(model(x), y).backward()
+
+    try:
+        for _ in range(4):
+            backprop()
+            ctl.iterate(backprop)
+    finally:
+        ctl.uninstall_hook()
+    out = capsys.readouterr().out
+    assert "Exact Variance" in out and "use 4 bit to compare" in out and "GACT: Initializing AutoPrec" in out
+    records = [json.loads(l) for l in (tmp_path / "autoprec.log").read_text().splitlines()]
+    # one record per iteration, plus the warning's own record at the adaptation of iteration 2 (> warm-up 0; the
+    # running gradient variance is still tiny then).  The recorder never forgets a key (its clear() is a no-op in
+    # the reference too), so the later records carry the warning's fields along.
+    assert [r["iter"] for r in records] == [0, 1, 2, 2, 3]
+    L = len(ctl.quantizer.bits)
+    for r in records:
+        assert len(r["layer sensitivity"]) == L and len(r["bits"]) == L and len(r["dims"]) == L
+    assert "warning" not in records[0] and "warning" not in records[1]
+    warned = records[2]
+    assert warned["warning"] is True and warned["quantization var"] > 0.1 * warned["overall var"]
+    assert "Quantization variance is too large" in out
+    assert ctl.ap.grad_var > 0 and 0 < ctl.ap.beta1 < 1
+    # debug leaves the allocated widths in place
+    assert ctl.quantizer.bits == ctl.ap.bits
+
+
+def test_python_layer_raises_when_a_pipeline_wait_ran_out(fake, monkeypatch):
+    import gact.controller
+    monkeypatch.setattr(gact.controller, "_device_live", lambda: True)
+    config.reset()
+    gact.set_optimization_level("L1")
+    ctl = Controller(TinyNet())
+    ctl.install_hook()
+    fake_native.FakeLib.pipeline_error = 2
+    try:
+        with pytest.raises(RuntimeError, match="pipeline"):
+            ctl.uninstall_hook()
+        assert fake_native.FakeLib.pipeline_error == 0 and not ctl._hook_installed      # reported once, then cleared
+        ctl.install_hook()
+        ctl.uninstall_hook()
+    finally:
+        fake_native.FakeLib.pipeline_error = 0
+    # and at the probe's synchronisation point
+    fake_native.FakeLib.pipeline_error = 1
+    try:
+        with pytest.raises(RuntimeError, match="pipeline"):
+            _train("L2", 1, interval=1)
+    finally:
+        fake_native.FakeLib.pipeline_error = 0
+
+
+def test_probe_refuses_gradients_of_different_size(fake):
+    _, ctl = _train("L2", 1, interval=100)
+    g = [torch.zeros(10), torch.zeros(5)]
+    with pytest.raises(RuntimeError, match="different total size"):
+        ctl.ap._distances(torch.zeros(15), torch.zeros(14), g, torch.zeros(3, dtype=torch.float64))
+    with pytest.raises(RuntimeError, match="different total size"):
+        ctl.ap._distances(torch.zeros(15), torch.zeros(15), g[:1], torch.zeros(3, dtype=torch.float64))
+
+
+def test_a_tid_that_was_a_duplicate_at_registration_can_stand_alone_later(fake):
+    q = Quantizer(4, False, False)
+    x = torch.randn(16, 256, requires_grad=True)
+    q.quantize(x); q.quantize(x)                 # iteration 0: tid 1 shares tid 0's payload and registers nothing
+    assert list(q.bits) == [0]
+    q.iterate()
+    a = q.quantize(x)
+    b = q.quantize(x.detach().clone().requires_grad_())      # tid 1 is its own tensor now
+    assert b[4] == 1 and q.ptr_qtensor_map[b[2]][0].bits == q.default_bit
+    q.dequantize(a); q.dequantize(b)
+
+
+def test_short_payloads_are_refused(fake, monkeypatch):
+    from gact import ops
+    import gact.cpp_extension.quantization as shim
+    monkeypatch.setattr(shim, "nv", fake_native.FakeNative)
+    x = torch.randn(3, 300)
+    q = ops.op_quantize(x, 4, 0)
+    with pytest.raises(ValueError):
+        ops.op_dequantize([q[0][:100], 4, q[2], q[3]], x.shape)
+    with pytest.raises(ValueError):
+        ops.op_dequantize([q[0], 4, q[2][:1], q[3]], x.shape)
+    m = (torch.rand(700) < 0.5).to(torch.uint8)
+    words, shape = ops.op_quantize_mask(m)
+    assert words.numel() == 32                                    # two started blocks of 512
+    with pytest.raises(ValueError):
+        ops.op_dequantize_mask([words[:22], shape])               # ceil(700/32) words, what the reference allocates
+    with pytest.raises(ValueError):
+        shim.act_dequantize_dropout_mask(words[:22], 700)
+    with pytest.raises(ValueError):
+        shim.unpack_single_precision(q[0][:64], 4, q[2], q[3], 4, 1, 256)
+    assert torch.equal(shim.act_dequantize_dropout_mask(words, 700), m)

@@ -13,6 +13,8 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
+
 pytestmark = pytest.mark.gpu
 
 
@@ -78,6 +80,57 @@ def test_noalloc_matches_existing_entry_point_twice_in_a_row():
     # and the first problem again: same answer as before
     got3 = _noalloc(nv, g0, g1, None, segs)
     torch.testing.assert_close(got3, want1, rtol=1e-6, atol=0)
+
+    # both also agree with the CPU oracle (double accumulation of fp32 differences, summation order free)
+    torch.testing.assert_close(got1, oracle.sq_diffs3(g0.cpu(), g1.cpu(), torch.cat([s.cpu() for s in segs])), rtol=1e-6, atol=0)
+    torch.testing.assert_close(got2, oracle.sq_diffs3(h0.cpu(), h1.cpu(), h2.cpu()), rtol=1e-6, atol=0)
+
+
+def test_noalloc_leaves_device_memory_as_it_found_it():
+    """What the entry point is for: once the library's kernels are loaded (first call), a call changes neither the
+    free memory the driver reports nor what torch's allocator holds."""
+    from gact import _native as nv
+    g = torch.Generator().manual_seed(3)
+    segs = [torch.randn(n, generator=g).cuda() for n in (1000, 1 << 18, 5)]
+    P = sum(s.numel() for s in segs)
+    g0, g1 = torch.randn(P, generator=g).cuda(), torch.randn(P, generator=g).cuda()
+    out = torch.zeros(3, dtype=torch.float64, device="cuda")
+    n = len(segs)
+    lens = [s.numel() for s in segs]
+    ptrs = (ctypes.c_uint64 * n)(*[s.data_ptr() for s in segs])
+    offs = (ctypes.c_int64 * n)(*np.cumsum([0] + lens[:-1]).tolist())
+    lens_c = (ctypes.c_int64 * n)(*lens)
+
+    def call():
+        for args in ((None, ctypes.addressof(ptrs), ctypes.addressof(offs), ctypes.addressof(lens_c), n),
+                     (segs[1].data_ptr(), None, None, None, 0)):
+            Pk = P if args[4] else segs[1].numel()
+            assert nv.lib.gact_sq_diffs3_noalloc(g0.data_ptr(), g1.data_ptr(), args[0], Pk, args[1], args[2], args[3], args[4],
+                                                 out.data_ptr(), _stream()) == 0
+        torch.cuda.synchronize()
+
+    call()                                              # loads the kernels, looks up the scratch address
+    free0, _ = torch.cuda.mem_get_info()
+    held0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"free device memory changed by {free0 - free1} bytes"
+    assert torch.cuda.memory_allocated() == held0 and torch.cuda.memory_reserved() == reserved0
+
+
+def test_noalloc_rejects_tables_that_do_not_tile_the_vector():
+    from gact import _native as nv
+    x = torch.zeros(64, device="cuda")
+    out = torch.zeros(3, dtype=torch.float64, device="cuda")
+    ptrs = (ctypes.c_uint64 * 2)(x.data_ptr(), x.data_ptr())
+    lens = (ctypes.c_int64 * 2)(32, 32)
+    for offs, want in (((0, 40), 5), ((0, 16), 5), ((8, 40), 5)):
+        o = (ctypes.c_int64 * 2)(*offs)
+        st = nv.lib.gact_sq_diffs3_noalloc(x.data_ptr(), x.data_ptr(), None, 64, ctypes.addressof(ptrs), ctypes.addressof(o),
+                                           ctypes.addressof(lens), 2, out.data_ptr(), _stream())
+        assert st == want
+    torch.cuda.synchronize()
 
 
 def test_noalloc_rejects_more_segments_than_its_table_holds():
