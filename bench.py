@@ -818,7 +818,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch of the training workloads (0 = the workload's own)")
     ap.add_argument("--layers", type=int, default=0, help="bert_large only: fewer encoder layers for quick runs")
     ap.add_argument("--autocast", default=None, choices=["bf16", "fp16", "off"], help="autocast type of the training workloads (default: the workload's own)")
-    ap.add_argument("--dp-probe", default="allreduce", choices=["allreduce", "local"])
+    ap.add_argument("--dp-probe", default="allreduce", choices=["allreduce", "local", "shard"])
     ap.add_argument("--bucket-mb", type=int, default=100, help="DDP gradient bucket size of the training workloads")
     ap.add_argument("--get-mem", action="store_true", help="training workloads: activation memory of a step and a batch ladder")
     ap.add_argument("--e2e-steps", type=int, default=8)

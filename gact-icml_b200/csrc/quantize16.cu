@@ -35,9 +35,8 @@
 
 namespace gact {
 
-constexpr int kTG = 8;                               // groups per warp tile
-constexpr int kTileElems = kTG * kGroup;             // 2048
-constexpr int kTileBytes = kTileElems * 2;           // 4096
+constexpr int kTGMax = 8;                            // groups per warp tile: 8, or 4 for tensors of few tiles
+constexpr int kTileBytesMax = kTGMax * kGroup * 2;   // 4096: a stage of a warp's ring
 #ifndef GACT_Q16_STAGES
 #define GACT_Q16_STAGES 2
 #endif
@@ -46,7 +45,7 @@ constexpr int kTileBytes = kTileElems * 2;           // 4096
 #endif
 constexpr int kStages = GACT_Q16_STAGES;
 constexpr int kWarps = kQThreads / 32;
-constexpr int kSmemBytes = kWarps * kStages * kTileBytes;   // 64 KB per block, 3 blocks per SM
+constexpr int kSmemBytes = kWarps * kStages * kTileBytesMax;   // 64 KB per block, 3 blocks per SM
 
 __device__ int g_pipeline_error = 0;
 
@@ -90,33 +89,24 @@ template <int DT> __device__ __forceinline__ uint32_t lane_min_negmax(const uint
     return pmin2<DT>(__byte_perm(lo, nh, 0x5410u), __byte_perm(lo, nh, 0x7632u));
 }
 
-// Warp reduction of the tile's eight (min, -max) words at once.  Exchanges at distance 16, 8 and 4 each halve the
-// number of words a lane still carries (a lane keeps the groups whose index bit matches its lane bit and hands the
-// others over); distances 2 and 1 finish the remaining word.  Lanes 4k .. 4k+3 return group k's word.
-template <int DT> __device__ __forceinline__ uint32_t tile_reduce(uint32_t (&v)[kTG], int lane) {
-    {
-        const bool up = (lane & 16) != 0;
+// Warp reduction of the tile's TG (min, -max) words at once.  The first log2(TG) exchanges (distance 16, 8, ...)
+// each halve the number of words a lane still carries (a lane keeps the groups whose index bit matches its lane bit
+// and hands the others over); the remaining distances finish the one word left.  With L = 32 / TG, lanes
+// L*k .. L*k + L-1 return group k's word.
+template <int DT, int TG> __device__ __forceinline__ uint32_t tile_reduce(uint32_t (&v)[TG], int lane) {
+    static_assert(TG == 4 || TG == 8, "tile of 4 or 8 groups");
+    int dist = 16;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const uint32_t keep = up ? v[i + 4] : v[i], send = up ? v[i] : v[i + 4];
-            v[i] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, 16));
+    for (int half = TG / 2; half >= 1; half >>= 1, dist >>= 1) {
+        const bool up = (lane & dist) != 0;
+#pragma unroll
+        for (int i = 0; i < half; i++) {
+            const uint32_t keep = up ? v[i + half] : v[i], send = up ? v[i] : v[i + half];
+            v[i] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, dist));
         }
     }
-    {
-        const bool up = (lane & 8) != 0;
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const uint32_t keep = up ? v[i + 2] : v[i], send = up ? v[i] : v[i + 2];
-            v[i] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, 8));
-        }
-    }
-    {
-        const bool up = (lane & 4) != 0;
-        const uint32_t keep = up ? v[1] : v[0], send = up ? v[0] : v[1];
-        v[0] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, 4));
-    }
-    v[0] = pmin2<DT>(v[0], __shfl_xor_sync(kFull, v[0], 2));
-    v[0] = pmin2<DT>(v[0], __shfl_xor_sync(kFull, v[0], 1));
+    for (; dist >= 1; dist >>= 1) v[0] = pmin2<DT>(v[0], __shfl_xor_sync(kFull, v[0], dist));
     return v[0];
 }
 
@@ -266,12 +256,15 @@ __device__ __forceinline__ void codes8(const uint32_t (&raw)[4], const GroupCons
 }
 
 // ---- one tile ---------------------------------------------------------------------------------------------------------
-// FULL: all 8 groups exist and are complete.
-template <int DT, int BITS, int RNG, bool FULL, class Src>
+// TG groups per tile (at least one row-block).  FULL: all of them exist and are complete.
+template <int DT, int BITS, int RNG, int TG, bool FULL, class Src>
 __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lane, const Src& src) {
+    constexpr int kTG = TG;
     constexpr int WPT = 8 / BITS, U = kTG / WPT;
+    constexpr int LPG = 32 / kTG;                           // lanes that end up with the same group's result
+    static_assert(U >= 1, "a tile holds whole row-blocks");
     const int64_t g0 = tile * kTG;
-    const int myk = lane >> 2;                              // the group whose min / max / scale this lane ends up with
+    const int myk = lane / LPG;                             // the group whose min / max / scale this lane ends up with
 
     // ---- pass 1: min, max, scale ----
     uint32_t v[kTG];
@@ -282,14 +275,14 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
         v[k] = lane_min_negmax<DT>(raw);
     }
     // the reference starts from +-1e30 in T, which is what remains of a group of NaNs
-    const uint32_t mnx = pmin2<DT>(tile_reduce<DT>(v, lane), start_pair<DT>());
+    const uint32_t mnx = pmin2<DT>(tile_reduce<DT, kTG>(v, lane), start_pair<DT>());
     float mn = pair_lo<DT>(mnx), mx = -pair_hi<DT>(mnx);
     // a zero extreme takes the sign the reference's reduction order gives it (rare; decided per group by the whole warp)
     const unsigned amb = __ballot_sync(kFull, zero_sign_ambiguous(mn, mx));
     if (amb) {
 #pragma unroll
         for (int k = 0; k < kTG; k++) {
-            if (amb & (0xFu << (4 * k))) {
+            if (amb & ((0xffffffffu >> (32 - LPG)) << (LPG * k))) {
                 uint32_t raw[4];
                 float vals[8];
                 src.load(k, raw);
@@ -312,7 +305,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
         w0 = __float_as_uint(mn);
         w1 = __float_as_uint(sc);
     }
-    if ((lane & 3) == 0 && (FULL || g0 + myk < a.G)) {
+    if ((lane & (LPG - 1)) == 0 && (FULL || g0 + myk < a.G)) {
         if constexpr (DT == GACT_F16) {
             ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 & 0xffffu);
             ((unsigned short*)a.qscale)[g0 + myk] = (unsigned short)(w0 >> 16);
@@ -341,7 +334,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             for (int ni = 0; ni < WPT; ni++) {
                 const int k = u * WPT + ni;
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, 4 * k);
+                gc.fetch(w0, w1, LPG * k);
                 uint32_t raw[4];
                 src.load(k, raw);
                 const bool present = FULL || g0 + k < a.G;
@@ -360,7 +353,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             for (int j = 0; j < 8; j++) acc[j] = 0;
             GroupConst<DT> gc[WPT];
 #pragma unroll
-            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, 4 * (u * WPT + ni));
+            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, LPG * (u * WPT + ni));
             const uint64_t gid0 = (uint64_t)r * kGroup + lane * 8;
 #pragma unroll
             for (int c = 0; c < (WPT + 3) / 4; c++) {
@@ -409,7 +402,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
                     for (int i = 0; i < 4; i++) nz[i] = Centred<DT, RNG>::value ? add2(p[i], splat2(-0.5f)) : p[i];
                 }
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, 4 * k);
+                gc.fetch(w0, w1, LPG * k);
                 uint32_t raw[4];
                 src.load(k, raw);
                 uint32_t cb[8];
@@ -449,14 +442,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-// bulk_tiles: the leading tiles that come through the rings (0 when x is not 16-byte aligned)
-template <int DT, int BITS, int RNG>
+// TG: groups per warp tile.  bulk_tiles: the leading tiles that come through the rings (0 when x is not 16-byte aligned)
+template <int DT, int BITS, int RNG, int TG>
 __global__ void __launch_bounds__(kQThreads, GACT_Q16_MINB) quantize16_kernel(const __grid_constant__ QuantArgs a, int64_t bulk_tiles) {
+    constexpr int kTileBytes = TG * kGroup * 2;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[kWarps][kStages];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t nw = (int64_t)gridDim.x * kWarps, gw = (int64_t)blockIdx.x * kWarps + warp;
-    const int64_t tiles = (a.G + kTG - 1) / kTG;
+    const int64_t tiles = (a.G + TG - 1) / TG;
 
     if (gw < bulk_tiles) {
         unsigned char* buf = smem + warp * (kStages * kTileBytes);
@@ -490,7 +484,7 @@ __global__ void __launch_bounds__(kQThreads, GACT_Q16_MINB) quantize16_kernel(co
                 return;
             }
             const SmemSrc src{buf + s * kTileBytes + lane * 16};
-            tile16<DT, BITS, RNG, true>(a, t, lane, src);
+            tile16<DT, BITS, RNG, TG, true>(a, t, lane, src);
             __syncwarp();                                        // every lane is done reading the stage
             const int64_t tn = t + kStages * nw;
             if (lane == 0 && tn < bulk_tiles) {
@@ -502,13 +496,17 @@ __global__ void __launch_bounds__(kQThreads, GACT_Q16_MINB) quantize16_kernel(co
     }
     // what the rings do not take: the ragged end, or everything when x is not 16-byte aligned
     for (int64_t t = bulk_tiles + gw; t < tiles; t += nw) {
-        const GlobalSrc<DT> src{a.x, a.n, t * kTG, lane, a.align};
-        tile16<DT, BITS, RNG, false>(a, t, lane, src);
+        const GlobalSrc<DT> src{a.x, a.n, t * TG, lane, a.align};
+        tile16<DT, BITS, RNG, TG, false>(a, t, lane, src);
     }
 }
 
-template <int DT, int BITS, int RNG>
-static int launch16(const QuantArgs& a, cudaStream_t s) {
+#ifndef GACT_Q16_SMALL_ROUNDS
+#define GACT_Q16_SMALL_ROUNDS 3
+#endif
+
+template <int DT, int BITS, int RNG, int TG>
+static int launch16_tg(const QuantArgs& a, cudaStream_t s) {
     // the shared-memory opt-in is a per-device attribute of the kernel: 0 = not set up, 1 = usable, -1 = refused
     static std::atomic<int> ready_on[kMaxDevices];
     static std::atomic<int> per_sm_cached{0};
@@ -516,23 +514,35 @@ static int launch16(const QuantArgs& a, cudaStream_t s) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return GACT_ERR_LAUNCH;
     int ready = ready_on[dev].load(std::memory_order_relaxed);
     if (ready == 0) {
-        ready = cudaFuncSetAttribute(quantize16_kernel<DT, BITS, RNG>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess ? 1 : -1;
+        ready = cudaFuncSetAttribute(quantize16_kernel<DT, BITS, RNG, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess ? 1 : -1;
         ready_on[dev].store(ready, std::memory_order_relaxed);
     }
     if (ready != 1) return GACT_ERR_LAUNCH;
     int per_sm = per_sm_cached.load(std::memory_order_relaxed);
     if (per_sm == 0) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize16_kernel<DT, BITS, RNG>, kQThreads, kSmemBytes) != cudaSuccess || per_sm < 1)
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize16_kernel<DT, BITS, RNG, TG>, kQThreads, kSmemBytes) != cudaSuccess || per_sm < 1)
             per_sm = 1;
         per_sm_cached.store(per_sm, std::memory_order_relaxed);
     }
-    const int64_t tiles = (a.G + kTG - 1) / kTG;
-    const int64_t bulk_tiles = a.align >= 16 ? a.n / kTileElems : 0;
+    const int64_t tiles = (a.G + TG - 1) / TG;
+    const int64_t bulk_tiles = a.align >= 16 ? a.n / (TG * kGroup) : 0;
     const int64_t resident = (int64_t)per_sm * sm_count();
     const int64_t want = (tiles + kWarps - 1) / kWarps;
     const int blocks = (int)(want < resident ? want : resident);
-    quantize16_kernel<DT, BITS, RNG><<<blocks, kQThreads, kSmemBytes, s>>>(a, bulk_tiles);
+    quantize16_kernel<DT, BITS, RNG, TG><<<blocks, kQThreads, kSmemBytes, s>>>(a, bulk_tiles);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
+}
+
+// Tile size by tensor size: tiles of 8 groups amortise the per-tile work best, but a tensor of only a few tiles per
+// resident warp (3552 warps on a B200) leaves the last round mostly idle; below GACT_Q16_SMALL_ROUNDS rounds of
+// 8-group tiles the tensor is cut into tiles of 4 groups instead (1-bit codes need 8 groups for one row-block).
+template <int DT, int BITS, int RNG>
+static int launch16(const QuantArgs& a, cudaStream_t s) {
+    if constexpr (BITS > 1) {
+        const int64_t warps = (int64_t)sm_count() * GACT_Q16_MINB * kWarps;
+        if (a.G < (int64_t)GACT_Q16_SMALL_ROUNDS * warps * 8) return launch16_tg<DT, BITS, RNG, 4>(a, s);
+    }
+    return launch16_tg<DT, BITS, RNG, 8>(a, s);
 }
 
 template <int DT, int BITS>

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "gact_mask_words": ([_i64], _i64),
     "gact_mask_pack": ([_vp, _i64, _vp, _vp, _vp], _i),
     "gact_mask_unpack": ([_vp, _i64, _vp, _vp], _i),
+    "gact_fingerprint": ([_vp, _i, _i64, _vp, _vp], _i),
     "gact_sq_diffs3_scratch_bytes": ([], _i64),
     "gact_sq_diffs3": ([_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _vp, _vp], _i),
     "gact_sq_diffs3_noalloc": ([_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i, _vp, _vp], _i),

@@ -101,7 +101,7 @@ class AutoPrecision:
         org_state = torch.get_rng_state().clone()
         self._setup_seed(self.iter)
         no_sync = getattr(self.model, "no_sync", None)
-        if config.dp_probe == "local" and _dist() is not None and no_sync is not None:
+        if config.dp_probe in ("local", "shard") and _dist() is not None and no_sync is not None:
             with no_sync():
                 backprop()
         else:
@@ -165,7 +165,15 @@ class AutoPrecision:
         L = len(tids)
         dev = None
         d3 = None
+        dist = _dist()
+        W = dist.get_world_size() if dist is not None else 1
+        # 'shard': every rank probes its own share of the tensors (no gradient all-reduce during the probes), so
+        # the 3L extra passes are split W ways instead of being repeated on every rank
+        sharded = config.dp_probe == "shard" and W > 1
+        rank = dist.get_rank() if sharded else 0
         for i, l in enumerate(tids):
+            if sharded and i % W != rank:
+                continue
             b = q.bits[l]
             q.bits[l] = 1
             self._run_backprop(backprop)
@@ -187,16 +195,18 @@ class AutoPrecision:
             q.bits[l] = b
         if L == 0:
             return
+        if d3 is None:                                    # a rank without a share (more ranks than tensors)
+            dev = self._device = next(self.model.parameters()).device
+            d3 = torch.zeros((L, 3), dtype=torch.float64, device=dev)
         # one exchange of L x 3 statistics keeps every rank's decisions identical
         scale = 1.0
-        dist = _dist()
-        if dist is not None and dist.get_world_size() > 1:
-            W = dist.get_world_size()
+        if W > 1:
             dist.all_reduce(d3, op=dist.ReduceOp.SUM)
             # 'allreduce': every rank measured the averaged gradient -> mean of identical numbers.
             # 'local': ranks measured their own gradients; the noise terms are independent across ranks, so
             # the squared distance of the averaged gradient is the sum of the local ones over W^2.
-            scale = 1.0 / (W * W) if config.dp_probe == "local" else 1.0 / W
+            # 'shard': one rank's local measurement stands for all W ranks' (equal in expectation), W * d / W^2.
+            scale = {"local": 1.0 / (W * W), "shard": 1.0 / W}.get(config.dp_probe, 1.0 / W)
         C_dev = torch.empty(L, dtype=torch.float32, device=dev)
         with nv.device_guard(C_dev):
             st = nv.lib.gact_sensitivity(d3.data_ptr(), scale, C_dev.data_ptr(), L, nv.stream_ptr())

@@ -52,6 +52,10 @@ class Quantizer:
         self._mask_flag = None
         # tensors compressed in this forward pass, by object identity: id -> (weak reference, version, key)
         self._live = {}
+        # config.check_dup: saves of this step by (address, dtype, shape, strides), merges made, device fingerprints
+        self._live_ptr, self._merged, self._fp_meta = {}, [], {}
+        self._fp_table = None
+        self.dup_report = {"merged": 0, "missed": 0}
 
     def filter_tensors(self, pairs):
         for _, v in pairs:
@@ -96,6 +100,9 @@ class Quantizer:
         self.unrelated_tensors = None
 
     def iterate(self):
+        if self._fp_meta:
+            self._check_fingerprints()
+        self._live_ptr, self._merged, self._fp_meta = {}, [], {}
         self.ptr_qtensor_map = {}
         self.layer_key_map = {}
         self._live = {}
@@ -104,13 +111,69 @@ class Quantizer:
         self.iter += 1
 
     def generate_tensor_key(self, t, tid):
+        """Key under which the payload of this save is stored; equal keys share one payload.
+
+        The reference (config.check_dup) builds the key from the data pointer, 100 evenly spaced values and the sum
+        of the tensor, reading both back to the host: a synchronisation per saved tensor.  Two saves can only get
+        the same key there if they sit at the same address, so for tensors on the GPU the same merges are decided
+        here without reading anything back: an earlier save of this step at the same address, with the same
+        dtype, shape and strides, whose tensor is still alive (so the address cannot have been reused) and whose
+        version counter has not moved (so the bytes cannot have changed) holds the same values.  The value
+        fingerprint itself is still taken - by a kernel, into a device table - and all fingerprints of a step come
+        back in ONE copy at iterate(), where every merge is verified and saves that had equal fingerprints but
+        could not be proven equal on the host are counted (dup_report)."""
         if config.check_dup:
-            # 100 evenly spaced values + the data pointer + the sum of the tensor
-            sample_cnt = min(100, t.numel())
-            key = uniform_sample(t, sample_cnt, add_dataptr=True)
-            key.append(t.sum().item())
-            return tuple(key)
+            if not t.is_cuda:
+                # host tensors: nothing to synchronise with; the reference's key as it is
+                sample_cnt = min(100, t.numel())
+                key = uniform_sample(t, sample_cnt, add_dataptr=True)
+                key.append(t.sum().item())
+                return tuple(key)
+            ident = (t.data_ptr(), t.dtype, tuple(t.shape), t.stride())
+            self._fingerprint(t, tid, ident)
+            seen = self._live_ptr.get(ident)
+            if seen is not None and seen[0]() is not None and seen[1] == t._version and seen[2] in self.ptr_qtensor_map:
+                self._merged.append((tid, seen[2]))
+                return seen[2]
+            self._live_ptr[ident] = (weakref.ref(t), t._version, tid)
+            return tid
         return tid
+
+    def _fingerprint(self, t, tid, ident):
+        """Enqueue the fingerprint of save `tid` into row `tid` of the device table (no read-back here)."""
+        from gact import _native as nv
+        if self._fp_table is None or self._fp_table.device != t.device or tid >= self._fp_table.shape[0]:
+            rows = max(1024, 2 * (tid + 1))
+            new = torch.zeros((rows, 2), dtype=torch.int64, device=t.device)
+            if self._fp_table is not None and self._fp_table.device == t.device:
+                new[:self._fp_table.shape[0]] = self._fp_table
+            self._fp_table = new
+        x = t if t.is_contiguous() else t.contiguous()
+        with nv.device_guard(x):
+            st = nv.lib.gact_fingerprint(x.data_ptr(), x.element_size(), x.numel(), self._fp_table[tid].data_ptr(), nv.stream_ptr())
+        nv.check(st, "gact_fingerprint")
+        self._fp_meta[tid] = ident
+
+    def _check_fingerprints(self):
+        """One read-back for the whole step: every merge made on the strength of address + version must also agree
+        in value, and saves with equal address and fingerprint that were kept apart are counted."""
+        meta, merges = self._fp_meta, self._merged
+        self._fp_meta, self._merged = {}, []                    # a failed check is reported once
+        if not meta:
+            return
+        n = max(meta) + 1
+        rows = self._fp_table[:n].tolist()                      # the step's only synchronisation for deduplication
+        self._fp_table.zero_()
+        for tid, first in merges:
+            if rows[tid] != rows[first]:
+                raise RuntimeError("check_dup: saves %d and %d shared a payload but their values differ "
+                                   "(a tensor was modified without its version counter moving)" % (first, tid))
+        groups = {}
+        for tid, ident in meta.items():
+            groups.setdefault((ident, tuple(rows[tid])), []).append(tid)
+        merged = {t for t, _ in merges}
+        missed = sum(len([t for t in g[1:] if t not in merged]) for g in groups.values())
+        self.dup_report = {"merged": len(merges), "missed": missed}
 
     def _quantize_mask(self, input):
         if input.dtype == torch.bool:

@@ -144,6 +144,16 @@ int gact_mask_pack(const uint8_t* x, int64_t n, uint32_t* words, int* not_binary
 int gact_mask_unpack(const uint32_t* words, int64_t n, uint8_t* out, void* stream);
 
 /*
+ * Fingerprint of a tensor for value-based deduplication, kept on the device: adds to out2[0] a hash of the
+ * min(n, 100) evenly spaced elements i * (n div count) and to out2[1] the sum of all elements' raw bit patterns,
+ * both as wrapping 64-bit integers (the caller zeroes out2 first; several tensors' fingerprints go to one table
+ * and come back to the host in one copy).  Replaces the per-tensor read-backs of the reference's dedup key
+ * (gact/gact/quantizer.py:85-93: uniform_sample(...).tolist() and t.sum().item(); gact/gact/utils.py:16-24).
+ *   x  n elements of elem_bytes (1, 2 or 4) bytes, aligned to the element size;  out2  two uint64, 8-byte aligned
+ */
+int gact_fingerprint(const void* x, int elem_bytes, int64_t n, uint64_t* out2, void* stream);
+
+/*
  * The three squared distances of the sensitivity probe, out3 = { |g0-g1|^2, |g0-g2|^2, |g1-g2|^2 } in
  * double.  Replaces the three `((ga - gb) ** 2).sum()` of gact/gact/autoprec.py:116-118.
  *   g0, g1  P floats each (contiguous snapshots)

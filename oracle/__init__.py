@@ -201,6 +201,26 @@ def sensitivity(d3) -> float:
     return sens
 
 
+def fingerprint(t: torch.Tensor):
+    """(hash of the sampled elements, sum of raw bit patterns) as the library's gact_fingerprint defines them: both
+    wrapping 64-bit sums; sample i at i * (n // cnt), cnt = min(n, 100), each hashed with the splitmix64 finaliser of
+    bits + 0x9E3779B97F4A7C15 * (i + 1).  The sample positions are the reference's (gact/gact/utils.py:16-24)."""
+    import numpy as np
+    raw = _cpu(t).reshape(-1).view({1: torch.uint8, 2: torch.int16, 4: torch.int32}[t.element_size()]).numpy()
+    raw = raw.view({1: np.uint8, 2: np.uint16, 4: np.uint32}[t.element_size()]).astype(np.uint64)
+    n = raw.size
+    if n == 0:
+        return 0, 0
+    cnt = min(n, 100)
+    idx = np.arange(cnt, dtype=np.int64) * (n // cnt)
+    with np.errstate(over="ignore"):
+        z = raw[idx] + np.uint64(0x9E3779B97F4A7C15) * (np.arange(cnt, dtype=np.uint64) + np.uint64(1))
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+        return int(z.sum(dtype=np.uint64)), int(raw.sum(dtype=np.uint64))
+
+
 def threads() -> int:
     """Host threads the quantize / dequantize loops use (OpenMP)."""
     return int(lib().oracle_threads())

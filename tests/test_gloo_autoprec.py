@@ -63,7 +63,7 @@ def _worker(rank, world, port, mode, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["allreduce", "local"])
+@pytest.mark.parametrize("mode", ["allreduce", "local", "shard"])
 def test_ranks_agree_on_sensitivities_and_bits(tmp_path, mode):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), mode, str(tmp_path)), nprocs=world, join=True)
