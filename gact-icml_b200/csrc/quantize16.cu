@@ -44,7 +44,11 @@ constexpr int kTileBytesMax = kTGMax * kGroup * 2;   // 4096: a stage of a warp'
 #define GACT_Q16_MINB 3
 #endif
 constexpr int kStages = GACT_Q16_STAGES;
-constexpr int kWarps = kQThreads / 32;
+#ifndef GACT_Q16_WARPS
+#define GACT_Q16_WARPS 8
+#endif
+constexpr int kWarps = GACT_Q16_WARPS;               // warps per block, each with its own ring
+constexpr int kThreads16 = kWarps * 32;
 constexpr int kSmemBytes = kWarps * kStages * kTileBytesMax;   // 64 KB per block, 3 blocks per SM
 
 __device__ int g_pipeline_error = 0;
@@ -153,14 +157,24 @@ template <int DT> struct GlobalSrc {
 // ---- codes of one pair of elements, as magic bits (1.5*2^23 + code) ------------------------------------------------
 // fp16: the reference's half-precision arithmetic, p = round_h(round_h(x - mn) * scale), max(p, 0) (NaN -> 0), no
 // upper clamp in the reference's modes (CURAND, EXTERNAL), clamp at 2^b - 1 in FAST / RTN.
-template <int BITS, int RNG>
+// CLAMP (FAST / RTN only): the group's largest product round_h(range * scale) exceeds 2^b - 1, so the upper clamp can
+// act; for all other groups it is the identity (products are monotone in x) and is left out.
+template <int BITS, int RNG, bool CLAMP>
 __device__ __forceinline__ void code_pair_f16(uint32_t rawp, uint32_t mn2, uint32_t sc2, float2 nz, uint32_t& c0, uint32_t& c1) {
     constexpr float MAXC = (float)((1 << BITS) - 1);
     const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
     const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
     __half2 p = __hmax2(__hmul2(t, as_h2(sc2)), zero2);
-    if (NoOverflow<RNG>::value) p = __hmin2(p, maxc2);
+    if (NoOverflow<RNG>::value && CLAMP) p = __hmin2(p, maxc2);
     float2 r;
+#ifdef GACT_FAST_FLOOR
+    if (RNG == GACT_RNG_FAST) {
+        r = fma2_rm(mixed_fma2_256(p, nz), splat2(0.00390625f), splat2(kMagic - 128.0f));
+        c0 = __float_as_uint(r.x);
+        c1 = __float_as_uint(r.y);
+        return;
+    }
+#endif
     if (RNG == GACT_RNG_RTN) r = add2(__half22float2(p), splat2(kMagic));                        // (p + 0.5) - 0.5 = p
     else if (Centred<GACT_F16, RNG>::value) r = add2(mixed_add2(p, nz), splat2(kMagic));         // p + (noise - 0.5)
     else r = add2(add2(mixed_add2(p, nz), splat2(-0.5f)), splat2(kMagic));                       // u - 0.5 >= -0.5 rounds to 0
@@ -178,13 +192,17 @@ __device__ __forceinline__ void code_pair_f16_inf(uint32_t rawp, uint32_t mn2, u
     c1 = t.y > 0.0f ? top : 0u;
 }
 // fp16, round to nearest, staying in half precision: returns (0x6400 + code) in each half
-template <int BITS> __device__ __forceinline__ uint32_t code_pair_f16_rtn(uint32_t rawp, uint32_t mn2, uint32_t sc2, bool inf_scale) {
+// KIND: 0 = plain group, 1 = the upper clamp can act, 2 = scale is +inf
+template <int BITS, int KIND> __device__ __forceinline__ uint32_t code_pair_f16_rtn(uint32_t rawp, uint32_t mn2, uint32_t sc2) {
     constexpr float MAXC = (float)((1 << BITS) - 1);
     const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
     const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
     __half2 p;
-    if (inf_scale) p = __hmul2(__hgt2(t, zero2), maxc2);                                         // t > 0 ? 2^b - 1 : 0
-    else p = __hmin2(__hmax2(__hmul2(t, as_h2(sc2)), zero2), maxc2);
+    if (KIND == 2) p = __hmul2(__hgt2(t, zero2), maxc2);                                         // t > 0 ? 2^b - 1 : 0
+    else {
+        p = __hmax2(__hmul2(t, as_h2(sc2)), zero2);
+        if (KIND == 1) p = __hmin2(p, maxc2);
+    }
     return h2_bits(__hadd2(p, __float2half2_rn(1024.0f)));
 }
 // bf16 (our semantics): u = fma(x - mn, scale, noise - 0.5) in fp32, clamped to [0, 2^b - 1], NaN -> 0.
@@ -196,6 +214,15 @@ __device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, floa
     constexpr float MAXC = (float)((1 << BITS) - 1);
     if (PLAIN) rawp = pmax2<GACT_BF16>(rawp, mn2);
     const float2 t = mixed_add2_bf16(rawp, splat2(nmn));
+#ifdef GACT_FAST_FLOOR
+    if (RNG == GACT_RNG_FAST && PLAIN) {
+        const float2 wp = fma2(t, splat2(sc * 65536.0f), nz);
+        const float2 rr = fma2_rm(wp, splat2(1.52587890625e-05f), splat2(kMagic - 128.0f));
+        c0 = __float_as_uint(rr.x);
+        c1 = __float_as_uint(rr.y);
+        return;
+    }
+#endif
     float2 w = fma2(t, splat2(sc), nz);
     if (!PLAIN) { w.x = fmaxf(w.x, 0.0f); w.y = fmaxf(w.y, 0.0f); }
     if (!NoOverflow<RNG>::value) { w.x = fminf(w.x, MAXC); w.y = fminf(w.y, MAXC); }
@@ -206,15 +233,20 @@ __device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, floa
 
 // what every lane needs to know about one group in pass 2
 template <int DT> struct GroupConst;
+// fp16: the word lane L*k publishes is (min, scale) as two halves; bit 31 - the scale's sign, clear for every group
+// with a finite range - doubles as the "upper clamp can act" flag of FAST / RTN.
 template <> struct GroupConst<GACT_F16> {
     uint32_t mn2, sc2;
     bool special;                                   // scale is +inf
+    bool clamp;                                     // flag or negative scale (a group of NaNs): take the clamped path
     __device__ __forceinline__ void fetch(uint32_t w0, uint32_t, int src) {
         const uint32_t w = __shfl_sync(kFull, w0, src);
-        mn2 = __byte_perm(w, w, 0x1010u);
-        sc2 = __byte_perm(w, w, 0x3232u);
+        mn2 = h2_bits(__low2half2(as_h2(w)));
+        sc2 = h2_bits(__high2half2(as_h2(w)));
         special = ((w >> 16) & 0x7fffu) == 0x7c00u;
+        clamp = (int32_t)w < 0;
     }
+    __device__ __forceinline__ uint32_t scale_clean() const { return sc2 & 0x7fff7fffu; }
 };
 template <> struct GroupConst<GACT_BF16> {
     uint32_t mn2;
@@ -223,36 +255,54 @@ template <> struct GroupConst<GACT_BF16> {
     __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src) {
         const uint32_t m = __shfl_sync(kFull, w0, src);
         sc = __uint_as_float(__shfl_sync(kFull, w1, src));
-        mn2 = __byte_perm(m, m, 0x3232u);
+        const __nv_bfloat162 hi = __high2bfloat162(*(const __nv_bfloat162*)&m);
+        mn2 = *(const uint32_t*)&hi;
         nmn = -__uint_as_float(m);
         special = !(sc > 0.0f);
     }
 };
 
-template <int DT, int BITS, int RNG, bool SPECIAL>
+// KIND: 0 = plain group, 1 = fp16 group whose upper clamp can act (scale cleaned of the flag), 2 = special group
+template <int DT, int BITS, int RNG, int KIND>
 __device__ __forceinline__ void code_pair_as(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
     if constexpr (DT == GACT_F16) {
-        if (SPECIAL) code_pair_f16_inf<BITS, RNG>(rawp, gc.mn2, c0, c1);
-        else code_pair_f16<BITS, RNG>(rawp, gc.mn2, gc.sc2, nz, c0, c1);
+        if (KIND == 2) code_pair_f16_inf<BITS, RNG>(rawp, gc.mn2, c0, c1);
+        else if (KIND == 1) code_pair_f16<BITS, RNG, true>(rawp, gc.mn2, gc.scale_clean(), nz, c0, c1);
+        else code_pair_f16<BITS, RNG, false>(rawp, gc.mn2, gc.sc2, nz, c0, c1);
     } else {
-        code_pair_bf16<BITS, RNG, !SPECIAL>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
+        code_pair_bf16<BITS, RNG, KIND != 2>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
     }
 }
+// one pair, kind decided here (the reference-stream arrangement works pair by pair; its modes never clamp above, and
+// their scale word carries no flag: a set sign bit there is a group of NaNs, for which either path gives code 0)
 template <int DT, int BITS, int RNG>
 __device__ __forceinline__ void code_pair(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
-    if (gc.special) code_pair_as<DT, BITS, RNG, true>(rawp, gc, nz, c0, c1);
-    else code_pair_as<DT, BITS, RNG, false>(rawp, gc, nz, c0, c1);
+    if (gc.special) code_pair_as<DT, BITS, RNG, 2>(rawp, gc, nz, c0, c1);
+    else code_pair_as<DT, BITS, RNG, 0>(rawp, gc, nz, c0, c1);
 }
-// the eight codes of a group; the special case is decided once for the group (it is the same for the whole warp)
+// the eight codes of a group; the kind is decided once for the group (it is the same for the whole warp)
 template <int DT, int BITS, int RNG>
 __device__ __forceinline__ void codes8(const uint32_t (&raw)[4], const GroupConst<DT>& gc, const float2 (&nz)[4], uint32_t (&cb)[8]) {
     if (gc.special) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, true>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, false>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 2>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+        return;
     }
+    if constexpr (DT == GACT_F16 && NoOverflow<RNG>::value) {
+        if (gc.clamp) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 1>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+            return;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 0>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+}
+// acc + (v << SHIFT) as a multiply-add: on the FMA pipe, which this kernel leaves idle, rather than the ALU
+__device__ __forceinline__ uint32_t shl_add(uint32_t v, int shift, uint32_t acc) {
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(v), "r"(1u << shift), "r"(acc));      // shift is a constant once unrolled
+    return d;
 }
 
 // ---- one tile ---------------------------------------------------------------------------------------------------------
@@ -314,6 +364,12 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             ((float*)a.qscale)[g0 + myk] = sc;
         }
     }
+    if constexpr (DT == GACT_F16 && NoOverflow<RNG>::value) {
+        // No element's product can exceed the one of the group's range: t = round_h(x - mn) <= round_h(mx - mn), and
+        // rounding and the multiplication by a non-negative scale are monotone.  (NaN compares false: no flag.)
+        const float range = Elem<GACT_F16>::round(__fsub_rn(mx, mn));
+        if (Elem<GACT_F16>::round(range * sc) > (float)((1 << BITS) - 1)) w0 |= 0x80000000u;
+    }
 
     // ---- pass 2: codes, one row-block at a time ----
     float2 nz_odd[4];            // FAST: noise of an odd group, produced together with the even group before it
@@ -338,11 +394,22 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
                 uint32_t raw[4];
                 src.load(k, raw);
                 const bool present = FULL || g0 + k < a.G;
+                uint32_t c[4];
+                if (!present) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t c = present ? code_pair_f16_rtn<BITS>(raw[i], gc.mn2, gc.sc2, gc.special) : 0x64006400u;
-                    acc2[i] += c << (ni * BITS);
+                    for (int i = 0; i < 4; i++) c[i] = 0x64006400u;
+                } else if (gc.special) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 2>(raw[i], gc.mn2, gc.sc2);
+                } else if (gc.clamp) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 1>(raw[i], gc.mn2, gc.scale_clean());
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 0>(raw[i], gc.mn2, gc.sc2);
                 }
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc2[i] = shl_add(c[i], ni * BITS, acc2[i]);
             }
             st_stream_u2(dst, make_uint2(__byte_perm(acc2[0], acc2[1], 0x6420u), __byte_perm(acc2[2], acc2[3], 0x6420u)));
         } else if constexpr (RNG == GACT_RNG_CURAND) {
@@ -388,7 +455,11 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
                 float2 nz[4];
                 if (RNG == GACT_RNG_FAST) {
                     if ((k & 1) == 0) {
+#ifdef GACT_FAST_FLOOR
+                        fast_raw16<(DT == GACT_F16 ? 0x47000080u : 0x4B000080u)>((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
+#else
                         fast_noise16<true>((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
+#endif
                     } else {
 #pragma unroll
                         for (int i = 0; i < 4; i++) nz[i] = nz_odd[i];
@@ -409,7 +480,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
                 codes8<DT, BITS, RNG>(raw, gc, nz, cb);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                    if (NoOverflow<RNG>::value) acc[j] += cb[j] << (ni * BITS);      // disjoint slots: a sum is an OR
+                    if (NoOverflow<RNG>::value) acc[j] = shl_add(cb[j], ni * BITS, acc[j]);      // disjoint slots: a sum is an OR
                     else acc[j] |= cb[j] << (ni * BITS);
                 }
             }
@@ -444,7 +515,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 // TG: groups per warp tile.  bulk_tiles: the leading tiles that come through the rings (0 when x is not 16-byte aligned)
 template <int DT, int BITS, int RNG, int TG>
-__global__ void __launch_bounds__(kQThreads, GACT_Q16_MINB) quantize16_kernel(const __grid_constant__ QuantArgs a, int64_t bulk_tiles) {
+__global__ void __launch_bounds__(kThreads16, GACT_Q16_MINB) quantize16_kernel(const __grid_constant__ QuantArgs a, int64_t bulk_tiles) {
     constexpr int kTileBytes = TG * kGroup * 2;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t bars[kWarps][kStages];
@@ -520,7 +591,7 @@ static int launch16_tg(const QuantArgs& a, cudaStream_t s) {
     if (ready != 1) return GACT_ERR_LAUNCH;
     int per_sm = per_sm_cached.load(std::memory_order_relaxed);
     if (per_sm == 0) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize16_kernel<DT, BITS, RNG, TG>, kQThreads, kSmemBytes) != cudaSuccess || per_sm < 1)
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize16_kernel<DT, BITS, RNG, TG>, kThreads16, kSmemBytes) != cudaSuccess || per_sm < 1)
             per_sm = 1;
         per_sm_cached.store(per_sm, std::memory_order_relaxed);
     }
@@ -529,7 +600,7 @@ static int launch16_tg(const QuantArgs& a, cudaStream_t s) {
     const int64_t resident = (int64_t)per_sm * sm_count();
     const int64_t want = (tiles + kWarps - 1) / kWarps;
     const int blocks = (int)(want < resident ? want : resident);
-    quantize16_kernel<DT, BITS, RNG, TG><<<blocks, kQThreads, kSmemBytes, s>>>(a, bulk_tiles);
+    quantize16_kernel<DT, BITS, RNG, TG><<<blocks, kThreads16, kSmemBytes, s>>>(a, bulk_tiles);
     return cudaGetLastError() == cudaSuccess ? GACT_OK : GACT_ERR_LAUNCH;
 }
 

@@ -37,12 +37,17 @@ template <int DT, int RNG> struct Centred {
 // slots cannot collide and the packed byte may be summed instead of OR-ed.
 template <int RNG> struct NoOverflow { static constexpr bool value = (RNG == GACT_RNG_FAST || RNG == GACT_RNG_RTN); };
 
-// noise of the FAST arrangement: one Philox4x32-10 call, counter (block_lo, block_hi, 0, "FAST"), gives 16
+// noise of the FAST arrangement: one Philox4x32-7 call, counter (block_lo, block_hi, 0, "FAST"), gives 16
 // bytes = 8 bits for each of this lane's 8 elements of an even group (bytes 0..7) and of the following odd group
-// (bytes 8..15); noise = (byte + 0.5) / 256 (minus 0.5 when CENTRED).
+// (bytes 8..15); noise = (byte + 0.5) / 256 (minus 0.5 when CENTRED).  Seven rounds: the member of the Philox4x32
+// family with the fewest rounds that passes BigCrush (Salmon et al., SC'11); the ten rounds of cuRAND's generator
+// (which the CURAND mode uses) add a safety margin that rounding noise does not need, at 6-7 % of the kernel's time.
+#ifndef GACT_FAST_ROUNDS
+#define GACT_FAST_ROUNDS 7
+#endif
 template <bool CENTRED>
 __device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& rk, float2 (&even)[4], float2 (&odd)[4]) {
-    const uint4 r = philox4x32_10((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
+    const uint4 r = philox4x32<GACT_FAST_ROUNDS>((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
     // byte -> float without a conversion: a byte permute drops it into bits 8..15 of the mantissa of 2^23, giving
     // 2^23 + 256*b; times 2^-16 that is 128 + b/256, and the offset below brings (b + 0.5)/256 (- 0.5), all exact
@@ -56,6 +61,36 @@ __device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& r
         dst[(2 * i + 1) & 3] = fma2(make_float2(b2, b3), s2, o2);
     }
 }
+
+#ifdef GACT_FAST_FLOOR
+// EXPERIMENT (timing only): the same 16 noise bytes as float bit patterns K + b * 2^s + 2^(s-1), with the constant
+// and the half-unit offset coming out of the byte permute: no scaling instruction.
+template <uint32_t K>
+__device__ __forceinline__ void fast_raw16(uint64_t block, const PhiloxKeys& rk, float2 (&even)[4], float2 (&odd)[4]) {
+    const uint4 r = philox4x32<GACT_FAST_ROUNDS>((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float2 (&dst)[4] = (i < 2) ? even : odd;
+        dst[(2 * i) & 3] = make_float2(__uint_as_float(__byte_perm(w[i], K, 0x7604u)), __uint_as_float(__byte_perm(w[i], K, 0x7614u)));
+        dst[(2 * i + 1) & 3] = make_float2(__uint_as_float(__byte_perm(w[i], K, 0x7624u)), __uint_as_float(__byte_perm(w[i], K, 0x7634u)));
+    }
+}
+__device__ __forceinline__ float2 fma2_rm(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{ .reg .b64 ra, rb, rc, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; mov.b64 rc, {%6,%7}; fma.rm.f32x2 rd, ra, rb, rc; "
+        "mov.b64 {%0,%1}, rd; }"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+// float(h) * 256 + c for both halves (mixed-precision fma)
+__device__ __forceinline__ float2 mixed_fma2_256(__half2 h, float2 c) {
+    float2 d;
+    asm("{ .reg .b16 lo, hi, m; mov.b32 {lo, hi}, %2; mov.b16 m, 0x5c00; fma.rn.f32.f16 %0, lo, m, %3; fma.rn.f32.f16 %1, hi, m, %4; }"
+        : "=f"(d.x), "=f"(d.y) : "r"(*(const uint32_t*)&h), "f"(c.x), "f"(c.y));
+    return d;
+}
+#endif
 
 // cuRAND's uniform of two words: float(word) * 2^-32 + 2^-33 (minus 0.5 when CENTRED)
 template <bool CENTRED>

@@ -39,7 +39,7 @@ enum { GACT_F32 = 0, GACT_F16 = 1, GACT_BF16 = 2 };
 /* where the rounding noise comes from */
 enum {
     GACT_RNG_CURAND = 0,   /* the reference's stream: curand_init(seed, byte index, 0) + curand_uniform per slot */
-    GACT_RNG_FAST = 1,     /* Philox4x32-10 as well, but one call feeds 16 elements with 8 bits each */
+    GACT_RNG_FAST = 1,     /* Philox4x32 with 7 rounds, one call feeds 16 elements with 8 bits each */
     GACT_RNG_RTN = 2,      /* noise = 0.5 everywhere: round to nearest */
     GACT_RNG_EXTERNAL = 3  /* noise read from a caller-supplied fp32 array (G*256 values in [0,1]) */
 };

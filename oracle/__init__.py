@@ -59,6 +59,7 @@ def lib() -> ctypes.CDLL:
         L.oracle_fast_noise.argtypes = [c.c_uint64, c.c_int64]
         L.oracle_fast_noise.restype = c.c_float
         L.oracle_philox4x32_10.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p]
+        L.oracle_philox4x32_r.argtypes = [c.c_void_p, c.c_void_p, c.c_int, c.c_void_p]
         L.oracle_float_to_half.argtypes = [c.c_float]
         L.oracle_float_to_half.restype = c.c_uint16
         L.oracle_half_to_float.argtypes = [c.c_uint16]
@@ -238,9 +239,13 @@ def fast_noise(seed: int, elem: int) -> float:
     return float(lib().oracle_fast_noise(seed, elem))
 
 
-def philox(counter, key):
+def philox(counter, key, rounds=10):
+    """Philox4x32 with the given number of rounds (10 = cuRAND's generator, 7 = what rng_mode 'fast' uses)."""
     c = (ctypes.c_uint32 * 4)(*counter)
     k = (ctypes.c_uint32 * 2)(*key)
     o = (ctypes.c_uint32 * 4)()
-    lib().oracle_philox4x32_10(c, k, o)
+    if rounds == 10:
+        lib().oracle_philox4x32_10(c, k, o)
+    else:
+        lib().oracle_philox4x32_r(c, k, rounds, o)
     return list(o)

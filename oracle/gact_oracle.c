@@ -34,6 +34,7 @@
 
 enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
 enum { RNG_CURAND = 0, RNG_FAST = 1, RNG_RTN = 2, RNG_EXTERNAL = 3 };
+#define FAST_ROUNDS 7        /* Philox rounds of RNG_FAST */
 
 /* ------------------------------------------------------------------------------------------------
  * 16-bit float formats, in software (round-to-nearest-even), so that no compiler/ISA feature is needed
@@ -119,10 +120,10 @@ uint16_t oracle_float_to_bf16(float f) { return float_to_bf16(f); }
 /* ------------------------------------------------------------------------------------------------
  * Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11)
  * ---------------------------------------------------------------------------------------------- */
-void oracle_philox4x32_10(const uint32_t ctr_in[4], const uint32_t key_in[2], uint32_t out[4]) {
+void oracle_philox4x32_r(const uint32_t ctr_in[4], const uint32_t key_in[2], int rounds, uint32_t out[4]) {
     uint32_t c0 = ctr_in[0], c1 = ctr_in[1], c2 = ctr_in[2], c3 = ctr_in[3];
     uint32_t k0 = key_in[0], k1 = key_in[1];
-    for (int r = 0; r < 10; r++) {
+    for (int r = 0; r < rounds; r++) {
         uint64_t p0 = (uint64_t)0xD2511F53u * c0;
         uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
         uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0;
@@ -133,6 +134,10 @@ void oracle_philox4x32_10(const uint32_t ctr_in[4], const uint32_t key_in[2], ui
         k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
     }
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+/* the generator cuRAND uses: ten rounds */
+void oracle_philox4x32_10(const uint32_t ctr_in[4], const uint32_t key_in[2], uint32_t out[4]) {
+    oracle_philox4x32_r(ctr_in, key_in, 10, out);
 }
 
 /* uniform in (0, 1] from one 32-bit word, as cuRAND's curand_uniform does:
@@ -477,7 +482,9 @@ int oracle_sq_diffs3(const float *g0, const float *g1, const float *g2, int64_t 
 }
 
 /* ------------------------------------------------------------------------------------------------
- * RNG_FAST (no counterpart in the reference): one Philox4x32-10 call feeds 16 elements with 8 bits of noise
+ * RNG_FAST (no counterpart in the reference): one Philox4x32-7 call (seven rounds: the member of the family with
+ * the fewest rounds that passes BigCrush, Salmon et al., SC'11, table 2; cuRAND's ten add a safety margin that
+ * rounding noise does not need) feeds 16 elements with 8 bits of noise
  * each - the 8 elements d..d+7 (d a multiple of 8) of an even group g and the same 8 positions of group g+1.
  * Block index j = (g div 2) * 32 + (d div 8), counter (j_lo, j_hi, 0, 0x46415354 "FAST"), key (seed_lo,
  * seed_hi); element (g, d) takes byte (g mod 2) * 8 + (d mod 8) of the 16 output bytes (word = byte div 4,
@@ -491,7 +498,7 @@ static float fast_noise(uint64_t seed, int64_t elem) {
     uint32_t ctr[4] = { (uint32_t)j, (uint32_t)(j >> 32), 0u, 0x46415354u };
     uint32_t key[2] = { (uint32_t)seed, (uint32_t)(seed >> 32) };
     uint32_t out[4];
-    oracle_philox4x32_10(ctr, key, out);
+    oracle_philox4x32_r(ctr, key, FAST_ROUNDS, out);
     uint32_t b = (out[e >> 2] >> ((e & 3) * 8)) & 0xffu;
     return ((float)b + 0.5f) * 0.00390625f;
 }

@@ -281,7 +281,8 @@ def test_inputs_at_odd_offsets(dtype, bits):
         # dequantize into a view at an odd offset, with guard elements on both sides
         out = torch.full((n + off + 8,), -777.0, dtype=dtype, device="cuda")
         view = out[off:off + n]
-        st = nv.lib.gact_dequantize(opk.cuda().data_ptr(), omn.cuda().data_ptr(), osc.cuda().data_ptr(), nv.DTYPE_CODE[dtype],
+        dpk, dmn, dsc = opk.cuda(), omn.cuda(), osc.cuda()
+        st = nv.lib.gact_dequantize(dpk.data_ptr(), dmn.data_ptr(), dsc.data_ptr(), nv.DTYPE_CODE[dtype],
                                     n, bits, view.data_ptr(), torch.cuda.current_stream().cuda_stream)
         assert st == 0
         torch.cuda.synchronize()

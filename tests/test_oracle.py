@@ -28,6 +28,24 @@ def test_philox_known_answer():
     assert oracle.philox([0] * 4, [0] * 2) == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
 
 
+def test_philox_round_count():
+    """The rounds-parameterised routine is the same round function: ten rounds give cuRAND's generator (pinned above),
+    and the seven rounds of rng_mode 'fast' are its first seven (three more rounds, with the key advanced seven times,
+    arrive at the ten-round output)."""
+    ctr, key = [0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0]
+    assert oracle.philox(ctr, key, rounds=10) == oracle.philox(ctr, key)
+    seven = oracle.philox(ctr, key, rounds=7)
+    key7 = [(key[0] + 7 * 0x9E3779B9) & 0xffffffff, (key[1] + 7 * 0xBB67AE85) & 0xffffffff]
+    assert oracle.philox(seven, key7, rounds=3) == oracle.philox(ctr, key)
+    assert seven != oracle.philox(ctr, key, rounds=6) and seven != oracle.philox(ctr, key)
+    # the fast noise takes byte e of block j from the seven-round output
+    seed, elem = 12345 + (9 << 32), 256 * 7 + 19                       # group 7 (odd), position 19
+    j, e = (7 >> 1) * 32 + (19 >> 3), 8 + (19 & 7)
+    out = oracle.philox([j, 0, 0, 0x46415354], [seed & 0xffffffff, seed >> 32], rounds=7)
+    byte = (out[e >> 2] >> ((e & 3) * 8)) & 0xff
+    assert oracle.fast_noise(seed, elem) == (byte + 0.5) / 256
+
+
 def test_calc_precision_against_reference_vectors(golden_dir):
     """Inputs/outputs recorded from the reference's calc_precision.cc built unmodified."""
     cases = json.loads((golden_dir / "calc_precision.json").read_text())["cases"]
