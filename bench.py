@@ -708,7 +708,7 @@ def run_training(args):
 
 def memory_ladder(args, dev, reference):
     """Batch ladder of `workloads.batch_ladder` for the current level: doubles the batch while the next rung is
-    predicted to stay below 90 % of the device memory."""
+    predicted to stay below 80 % of the device memory (reserved by the caching allocator, which runs ahead of what is allocated)."""
     import workloads
     gact = import_gact(reference)
     from gact.controller import Controller
@@ -724,7 +724,7 @@ def memory_ladder(args, dev, reference):
         return wl, (lambda: ctl.iterate(wl.backprop)), ctl.uninstall_hook
 
     start = args.batch or {"bert_large": 64, "resnet50": 256}[args.workload]
-    return workloads.batch_ladder(build, start, int(0.9 * total))
+    return workloads.batch_ladder(build, start, int(0.8 * total))
 
 
 # ----------------------------------------------------------------------------------------------------------------

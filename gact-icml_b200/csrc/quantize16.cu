@@ -233,18 +233,18 @@ __device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, floa
 
 // what every lane needs to know about one group in pass 2
 template <int DT> struct GroupConst;
-// fp16: the word lane L*k publishes is (min, scale) as two halves; bit 31 - the scale's sign, clear for every group
-// with a finite range - doubles as the "upper clamp can act" flag of FAST / RTN.
+// fp16: lane L*k publishes min and scale, each already doubled into both halves of a word, so that pass 2 gets its
+// two-wide operands with two shuffles and no further instruction.  Which groups are special (scale +inf) and which
+// need the upper clamp of FAST / RTN travels as two ballot masks (bit L*k = group k): warp-uniform values.
 template <> struct GroupConst<GACT_F16> {
     uint32_t mn2, sc2;
     bool special;                                   // scale is +inf
-    bool clamp;                                     // flag or negative scale (a group of NaNs): take the clamped path
-    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t, int src) {
-        const uint32_t w = __shfl_sync(kFull, w0, src);
-        mn2 = h2_bits(__low2half2(as_h2(w)));
-        sc2 = h2_bits(__high2half2(as_h2(w)));
-        special = ((w >> 16) & 0x7fffu) == 0x7c00u;
-        clamp = (int32_t)w < 0;
+    bool clamp;                                     // the upper clamp can act (or the group is all NaN)
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask, unsigned cmask) {
+        mn2 = __shfl_sync(kFull, w0, src);
+        sc2 = __shfl_sync(kFull, w1, src);
+        special = (smask >> src) & 1u;
+        clamp = (cmask >> src) & 1u;
     }
     __device__ __forceinline__ uint32_t scale_clean() const { return sc2 & 0x7fff7fffu; }
 };
@@ -252,13 +252,13 @@ template <> struct GroupConst<GACT_BF16> {
     uint32_t mn2;
     float nmn, sc;
     bool special;                                   // not (scale > 0): the group holds an infinity, or only NaN
-    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src) {
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask, unsigned) {
         const uint32_t m = __shfl_sync(kFull, w0, src);
         sc = __uint_as_float(__shfl_sync(kFull, w1, src));
         const __nv_bfloat162 hi = __high2bfloat162(*(const __nv_bfloat162*)&m);
         mn2 = *(const uint32_t*)&hi;
         nmn = -__uint_as_float(m);
-        special = !(sc > 0.0f);
+        special = (smask >> src) & 1u;
     }
 };
 
@@ -273,8 +273,7 @@ __device__ __forceinline__ void code_pair_as(uint32_t rawp, const GroupConst<DT>
         code_pair_bf16<BITS, RNG, KIND != 2>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
     }
 }
-// one pair, kind decided here (the reference-stream arrangement works pair by pair; its modes never clamp above, and
-// their scale word carries no flag: a set sign bit there is a group of NaNs, for which either path gives code 0)
+// one pair, kind decided here (the reference-stream arrangement works pair by pair; its modes never clamp above)
 template <int DT, int BITS, int RNG>
 __device__ __forceinline__ void code_pair(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
     if (gc.special) code_pair_as<DT, BITS, RNG, 2>(rawp, gc, nz, c0, c1);
@@ -346,30 +345,36 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
         }
     }
     float sc;
-    uint32_t w0, w1 = 0;                                    // what pass 2 fetches from lane 4k
+    uint32_t w0, w1;                                        // what pass 2 fetches from lane L*k
+    bool special, clampable = false;
     if constexpr (DT == GACT_F16) {
         sc = scale_f16<BITS>(mn, mx);
-        w0 = h2_bits(__floats2half2_rn(mn, sc));            // both are half-precision values already
+        w0 = h2_bits(__float2half2_rn(mn));                 // both are half-precision values already
+        w1 = h2_bits(__float2half2_rn(sc));
+        special = (w1 & 0x7fffu) == 0x7c00u;
+        if constexpr (NoOverflow<RNG>::value) {
+            // No element's product can exceed the one of the group's range: t = round_h(x - mn) <= round_h(mx - mn), and
+            // rounding and the multiplication by a non-negative scale are monotone (NaN compares false).  A negative
+            // scale only comes out of a group of NaNs; it takes the clamped path too, with the sign removed.
+            const float range = Elem<GACT_F16>::round(__fsub_rn(mx, mn));
+            clampable = Elem<GACT_F16>::round(range * sc) > (float)((1 << BITS) - 1) || (int32_t)w1 < 0;
+        }
     } else {
         sc = compute_scale<DT>(mn, mx, BITS);
         w0 = __float_as_uint(mn);
         w1 = __float_as_uint(sc);
+        special = !(sc > 0.0f);
     }
     if ((lane & (LPG - 1)) == 0 && (FULL || g0 + myk < a.G)) {
         if constexpr (DT == GACT_F16) {
             ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 & 0xffffu);
-            ((unsigned short*)a.qscale)[g0 + myk] = (unsigned short)(w0 >> 16);
+            ((unsigned short*)a.qscale)[g0 + myk] = (unsigned short)(w1 & 0xffffu);
         } else {
             ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 >> 16);
             ((float*)a.qscale)[g0 + myk] = sc;
         }
     }
-    if constexpr (DT == GACT_F16 && NoOverflow<RNG>::value) {
-        // No element's product can exceed the one of the group's range: t = round_h(x - mn) <= round_h(mx - mn), and
-        // rounding and the multiplication by a non-negative scale are monotone.  (NaN compares false: no flag.)
-        const float range = Elem<GACT_F16>::round(__fsub_rn(mx, mn));
-        if (Elem<GACT_F16>::round(range * sc) > (float)((1 << BITS) - 1)) w0 |= 0x80000000u;
-    }
+    const unsigned smask = __ballot_sync(kFull, special), cmask = __ballot_sync(kFull, clampable);
 
     // ---- pass 2: codes, one row-block at a time ----
     float2 nz_odd[4];            // FAST: noise of an odd group, produced together with the even group before it
@@ -390,7 +395,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             for (int ni = 0; ni < WPT; ni++) {
                 const int k = u * WPT + ni;
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, LPG * k);
+                gc.fetch(w0, w1, LPG * k, smask, cmask);
                 uint32_t raw[4];
                 src.load(k, raw);
                 const bool present = FULL || g0 + k < a.G;
@@ -420,7 +425,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             for (int j = 0; j < 8; j++) acc[j] = 0;
             GroupConst<DT> gc[WPT];
 #pragma unroll
-            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, LPG * (u * WPT + ni));
+            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, LPG * (u * WPT + ni), smask, cmask);
             const uint64_t gid0 = (uint64_t)r * kGroup + lane * 8;
 #pragma unroll
             for (int c = 0; c < (WPT + 3) / 4; c++) {
@@ -473,7 +478,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
                     for (int i = 0; i < 4; i++) nz[i] = Centred<DT, RNG>::value ? add2(p[i], splat2(-0.5f)) : p[i];
                 }
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, LPG * k);
+                gc.fetch(w0, w1, LPG * k, smask, cmask);
                 uint32_t raw[4];
                 src.load(k, raw);
                 uint32_t cb[8];
@@ -573,7 +578,7 @@ __global__ void __launch_bounds__(kThreads16, GACT_Q16_MINB) quantize16_kernel(c
 }
 
 #ifndef GACT_Q16_SMALL_ROUNDS
-#define GACT_Q16_SMALL_ROUNDS 3
+#define GACT_Q16_SMALL_ROUNDS 2
 #endif
 
 template <int DT, int BITS, int RNG, int TG>
@@ -605,7 +610,7 @@ static int launch16_tg(const QuantArgs& a, cudaStream_t s) {
 }
 
 // Tile size by tensor size: tiles of 8 groups amortise the per-tile work best, but a tensor of only a few tiles per
-// resident warp (3552 warps on a B200) leaves the last round mostly idle; below GACT_Q16_SMALL_ROUNDS rounds of
+// resident warp (3552 warps on a B200) leaves the last round mostly idle; below GACT_Q16_SMALL_ROUNDS (two) rounds of
 // 8-group tiles the tensor is cut into tiles of 4 groups instead (1-bit codes need 8 groups for one row-block).
 template <int DT, int BITS, int RNG>
 static int launch16(const QuantArgs& a, cudaStream_t s) {

@@ -242,17 +242,20 @@ def activation_memory(wl: Workload, iterate: Callable[[], None] = None) -> dict:
     torch.cuda.synchronize()
     after = torch.cuda.memory_allocated()
     return {"activation_bytes": int(act), "before_forward_bytes": int(init), "before_backward_bytes": int(before_backward),
-            "after_step_bytes": int(after), "peak_bytes": int(torch.cuda.max_memory_allocated())}
+            "after_step_bytes": int(after), "peak_bytes": int(torch.cuda.max_memory_allocated()),
+            "peak_reserved_bytes": int(torch.cuda.max_memory_reserved())}
 
 
 def batch_ladder(build: Callable[[int], tuple], start: int, limit_bytes: int, max_rungs: int = 12) -> list:
-    """Doubles the batch while the NEXT rung is predicted to stay below ``limit_bytes`` (a linear fit of the peak over
-    the rungs measured so far), instead of the reference's search by running out of memory
+    """Doubles the batch while the NEXT rung is predicted to stay below ``limit_bytes`` (a linear fit of the peak of
+    reserved memory over the rungs measured so far), instead of the reference's search by running out of memory
     (benchmark/vision/exp_mem_speed.py:42-54).  ``build(batch)`` -> (workload, iterate or None, cleanup); every rung
     runs two steps and reports the second.  Returns one record per rung; the last carries ``predicted_max_batch``."""
     rungs = []
     b = start
     for _ in range(max_rungs):
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
         wl, iterate, cleanup = build(b)
         try:
             wl.step()
@@ -265,13 +268,23 @@ def batch_ladder(build: Callable[[int], tuple], start: int, limit_bytes: int, ma
             torch.cuda.empty_cache()
         m["batch"] = b
         rungs.append(m)
+        # what decides whether the next rung fits is what the caching allocator has to RESERVE (its blocks fragment:
+        # reserved memory runs well ahead of allocated memory at large batches), so the prediction is made on that
         if len(rungs) >= 2:
-            (b0, p0), (b1, p1) = [(r["batch"], r["peak_bytes"]) for r in rungs[-2:]]
+            (b0, p0), (b1, p1) = [(r["batch"], r["peak_reserved_bytes"]) for r in rungs[-2:]]
             slope = max((p1 - p0) / (b1 - b0), 1.0)
         else:
-            slope = max((m["activation_bytes"] * 1.3) / b, 1.0)          # first guess: activations dominate the growth
-        fixed = m["peak_bytes"] - slope * b
+            slope = max((m["activation_bytes"] * 1.5) / b, 1.0)          # first guess: activations dominate the growth
+        fixed = m["peak_reserved_bytes"] - slope * b
         m["predicted_max_batch"] = int((limit_bytes - fixed) // slope)
+        # the same fit on ALLOCATED memory: what a run with a defragmenting allocator could reach, and the figure
+        # to compare between levels (fragmentation differs from level to level)
+        if len(rungs) >= 2:
+            (b0, p0), (b1, p1) = [(r["batch"], r["peak_bytes"]) for r in rungs[-2:]]
+            aslope = max((p1 - p0) / (b1 - b0), 1.0)
+        else:
+            aslope = slope
+        m["predicted_max_batch_by_allocated"] = int((limit_bytes - (m["peak_bytes"] - aslope * b)) // aslope)
         if fixed + slope * 2 * b > limit_bytes:
             break
         b *= 2

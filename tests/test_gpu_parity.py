@@ -219,9 +219,11 @@ WARPS = 148 * 3 * 8                 # resident warps of a full launch on a B200
 def test_tile_and_wave_boundaries(dtype, bits):
     """Whole tiles only / one group more / a ragged end; fewer tiles than a block has warps; one tile fewer, as many
     and one more than the resident warps (where a warp's second stage comes into use), and twice that plus one
-    (where the first stage is refilled)."""
+    (where the first stage is refilled); the group counts either side of the switch from 4- to 8-group tiles."""
+    small = 2 * WARPS * 8                 # groups: below this many a tensor is cut into tiles of 4 groups, from here on of 8
     sizes = [TILE, TILE + 256, TILE - 1, 3 * TILE + 5 * 256 + 77, 8 * TILE, 9 * TILE + 1,
-             (WARPS - 1) * TILE, WARPS * TILE + 100, (WARPS + 1) * TILE + 256 * 3, (2 * WARPS + 1) * TILE + 19]
+             (WARPS - 1) * TILE, WARPS * TILE + 100, (WARPS + 1) * TILE + 256 * 3, (2 * WARPS + 1) * TILE + 19,
+             (small - 1) * 256 + 5, small * 256, (small + 1) * 256 - 3]
     for j, n in enumerate(sizes):
         check_case(make_input("relu" if j % 2 else "randn", n, dtype, seed=j), bits, 3 + j, "fast")
     check_case(make_input("randn", (2 * WARPS + 1) * TILE + 19, dtype, seed=5), bits, 1, "rtn")
