@@ -39,14 +39,18 @@ def random_sample(input, sample_cnt, add_dataptr=True):
     return key
 
 
+_MB = float(1 << 20)
+
+
 def get_memory_usage(print_info=False):
-    """Bytes currently allocated by torch on the GPU (reference: gact/gact/utils.py:40-47)."""
-    allocated = torch.cuda.memory_allocated()
-    reserved = torch.cuda.memory_reserved()
+    """Bytes torch currently holds allocated on the GPU; with ``print_info`` also prints that figure and the bytes
+    its caching allocator has reserved, in the two-line format the reference's drivers print
+    (reference: gact/gact/utils.py:40-47)."""
+    in_use = torch.cuda.memory_allocated()
     if print_info:
-        print("allocated: %.2f MB" % (allocated / 1024 / 1024), flush=True)
-        print("reserved:  %.2f MB" % (reserved / 1024 / 1024), flush=True)
-    return allocated
+        for label, nbytes in (("allocated: ", in_use), ("reserved:  ", torch.cuda.memory_reserved())):
+            print("%s%.2f MB" % (label, nbytes / _MB), flush=True)
+    return in_use
 
 
 _ITEMSIZE = {
@@ -73,34 +77,42 @@ def compute_tensor_bytes(tensors):
 
 
 def empty_cache(ratio):
+    """Hand the caching allocator's unused blocks back to the driver when less than ``ratio`` of what it has
+    reserved on device 0 is in use (reference: gact/gact/utils.py:72-78); ``None`` switches the check off."""
     if ratio is None:
         return
-    allocated = torch.cuda.memory_allocated(0)
     reserved = torch.cuda.memory_reserved(0)
-    if reserved > 0 and allocated / reserved < ratio:
+    if reserved > 0 and torch.cuda.memory_allocated(0) < ratio * reserved:
         torch.cuda.empty_cache()
 
 
 class GlobalExpRecorder:
-    """Key/value recorder appended to a JSON-lines file (reference: gact/gact/utils.py:80-101)."""
+    """Key/value recorder whose current contents are appended to a file as one JSON line per ``dump``
+    (reference: gact/gact/utils.py:80-101).  Keys stay until they are overwritten: ``clear`` does nothing, as in the
+    reference, whose drivers rely on earlier keys still being there at the next dump."""
+
+    _INT_TYPES = (np.int32, np.int64)
+    _FLOAT_TYPES = (float, np.float32, np.float64)
 
     def __init__(self):
         self.val_dict = OrderedDict()
 
     def record(self, key, value, float_round=6):
-        if isinstance(value, (np.int32, np.int64)):
+        # numpy scalars are not JSON-serialisable; floats are rounded so that the log stays readable
+        if isinstance(value, self._INT_TYPES):
             value = int(value)
-        if isinstance(value, (float, np.float32, np.float64)):
+        elif isinstance(value, self._FLOAT_TYPES):
             value = round(float(value), float_round)
         self.val_dict[key] = value
 
     def dump(self, filename):
+        line = json.dumps(self.val_dict)
         with open(filename, "a") as fout:
-            fout.write(json.dumps(self.val_dict) + '\n')
+            fout.write(line + "\n")
         print("Save exp results to %s" % filename)
 
     def clear(self):
-        pass
+        return None
 
 
 exp_recorder = GlobalExpRecorder()
