@@ -391,7 +391,10 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16/bf16 in, u8 codes", "data": "synthetic",
             "config": {"workload": "kernel sweep: relu 128x64x112x112 fp16+bf16 x bits{1,2,4,8} + 50 mixed fp16 tensors 2^20..2^26 x bits{2,4,8}",
-                       "group_size": GROUP, "rng": args.rng, "l2": "inputs larger than L2; all quantizes of a pass run before its dequantizes",
+                       "group_size": GROUP, "rng": args.rng,
+                       "rng_note": "fast = the library's default noise arrangement (Philox4x32-7, 8 bits per element), not the reference's stream; "
+                                   "rng=curand reproduces the reference's bytes and is timed in `kernels` (quantize_curand_*)",
+                       "l2": "inputs larger than L2; all quantizes of a pass run before its dequantizes",
                        "passes_per_step": R, "bytes_per_pass_per_gpu": pass_bytes, "bytes_per_step_per_gpu": pass_bytes * R},
             "pct_of_8TBps": round(100 * value / world / 8000.0, 1),
             "roofline": {"kernel": "quantize16_kernel<f16, 2 bit, %s> on relu 128x64x112x112 (%d launches timed inside the steps)" % (args.rng, n_dom),

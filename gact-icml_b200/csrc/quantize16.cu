@@ -157,15 +157,13 @@ template <int DT> struct GlobalSrc {
 // ---- codes of one pair of elements, as magic bits (1.5*2^23 + code) ------------------------------------------------
 // fp16: the reference's half-precision arithmetic, p = round_h(round_h(x - mn) * scale), max(p, 0) (NaN -> 0), no
 // upper clamp in the reference's modes (CURAND, EXTERNAL), clamp at 2^b - 1 in FAST / RTN.
-// CLAMP (FAST / RTN only): the group's largest product round_h(range * scale) exceeds 2^b - 1, so the upper clamp can
-// act; for all other groups it is the identity (products are monotone in x) and is left out.
-template <int BITS, int RNG, bool CLAMP>
+template <int BITS, int RNG>
 __device__ __forceinline__ void code_pair_f16(uint32_t rawp, uint32_t mn2, uint32_t sc2, float2 nz, uint32_t& c0, uint32_t& c1) {
     constexpr float MAXC = (float)((1 << BITS) - 1);
     const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
     const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
     __half2 p = __hmax2(__hmul2(t, as_h2(sc2)), zero2);
-    if (NoOverflow<RNG>::value && CLAMP) p = __hmin2(p, maxc2);
+    if (NoOverflow<RNG>::value) p = __hmin2(p, maxc2);
     float2 r;
 #ifdef GACT_FAST_FLOOR
     if (RNG == GACT_RNG_FAST) {
@@ -192,17 +190,13 @@ __device__ __forceinline__ void code_pair_f16_inf(uint32_t rawp, uint32_t mn2, u
     c1 = t.y > 0.0f ? top : 0u;
 }
 // fp16, round to nearest, staying in half precision: returns (0x6400 + code) in each half
-// KIND: 0 = plain group, 1 = the upper clamp can act, 2 = scale is +inf
-template <int BITS, int KIND> __device__ __forceinline__ uint32_t code_pair_f16_rtn(uint32_t rawp, uint32_t mn2, uint32_t sc2) {
+template <int BITS, bool INF_SCALE> __device__ __forceinline__ uint32_t code_pair_f16_rtn(uint32_t rawp, uint32_t mn2, uint32_t sc2) {
     constexpr float MAXC = (float)((1 << BITS) - 1);
     const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
     const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
     __half2 p;
-    if (KIND == 2) p = __hmul2(__hgt2(t, zero2), maxc2);                                         // t > 0 ? 2^b - 1 : 0
-    else {
-        p = __hmax2(__hmul2(t, as_h2(sc2)), zero2);
-        if (KIND == 1) p = __hmin2(p, maxc2);
-    }
+    if (INF_SCALE) p = __hmul2(__hgt2(t, zero2), maxc2);                                         // t > 0 ? 2^b - 1 : 0
+    else p = __hmin2(__hmax2(__hmul2(t, as_h2(sc2)), zero2), maxc2);
     return h2_bits(__hadd2(p, __float2half2_rn(1024.0f)));
 }
 // bf16 (our semantics): u = fma(x - mn, scale, noise - 0.5) in fp32, clamped to [0, 2^b - 1], NaN -> 0.
@@ -234,25 +228,22 @@ __device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, floa
 // what every lane needs to know about one group in pass 2
 template <int DT> struct GroupConst;
 // fp16: lane L*k publishes min and scale, each already doubled into both halves of a word, so that pass 2 gets its
-// two-wide operands with two shuffles and no further instruction.  Which groups are special (scale +inf) and which
-// need the upper clamp of FAST / RTN travels as two ballot masks (bit L*k = group k): warp-uniform values.
+// two-wide operands with two shuffles and no further instruction.  Which groups are special (scale +inf) travels as
+// a ballot mask (bit L*k = group k): a warp-uniform value.
 template <> struct GroupConst<GACT_F16> {
     uint32_t mn2, sc2;
     bool special;                                   // scale is +inf
-    bool clamp;                                     // the upper clamp can act (or the group is all NaN)
-    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask, unsigned cmask) {
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask) {
         mn2 = __shfl_sync(kFull, w0, src);
         sc2 = __shfl_sync(kFull, w1, src);
         special = (smask >> src) & 1u;
-        clamp = (cmask >> src) & 1u;
     }
-    __device__ __forceinline__ uint32_t scale_clean() const { return sc2 & 0x7fff7fffu; }
 };
 template <> struct GroupConst<GACT_BF16> {
     uint32_t mn2;
     float nmn, sc;
     bool special;                                   // not (scale > 0): the group holds an infinity, or only NaN
-    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask, unsigned) {
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask) {
         const uint32_t m = __shfl_sync(kFull, w0, src);
         sc = __uint_as_float(__shfl_sync(kFull, w1, src));
         const __nv_bfloat162 hi = __high2bfloat162(*(const __nv_bfloat162*)&m);
@@ -262,40 +253,31 @@ template <> struct GroupConst<GACT_BF16> {
     }
 };
 
-// KIND: 0 = plain group, 1 = fp16 group whose upper clamp can act (scale cleaned of the flag), 2 = special group
-template <int DT, int BITS, int RNG, int KIND>
+template <int DT, int BITS, int RNG, bool SPECIAL>
 __device__ __forceinline__ void code_pair_as(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
     if constexpr (DT == GACT_F16) {
-        if (KIND == 2) code_pair_f16_inf<BITS, RNG>(rawp, gc.mn2, c0, c1);
-        else if (KIND == 1) code_pair_f16<BITS, RNG, true>(rawp, gc.mn2, gc.scale_clean(), nz, c0, c1);
-        else code_pair_f16<BITS, RNG, false>(rawp, gc.mn2, gc.sc2, nz, c0, c1);
+        if (SPECIAL) code_pair_f16_inf<BITS, RNG>(rawp, gc.mn2, c0, c1);
+        else code_pair_f16<BITS, RNG>(rawp, gc.mn2, gc.sc2, nz, c0, c1);
     } else {
-        code_pair_bf16<BITS, RNG, KIND != 2>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
+        code_pair_bf16<BITS, RNG, !SPECIAL>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
     }
 }
-// one pair, kind decided here (the reference-stream arrangement works pair by pair; its modes never clamp above)
+// one pair, kind decided here (the reference-stream arrangement works pair by pair)
 template <int DT, int BITS, int RNG>
 __device__ __forceinline__ void code_pair(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
-    if (gc.special) code_pair_as<DT, BITS, RNG, 2>(rawp, gc, nz, c0, c1);
-    else code_pair_as<DT, BITS, RNG, 0>(rawp, gc, nz, c0, c1);
+    if (gc.special) code_pair_as<DT, BITS, RNG, true>(rawp, gc, nz, c0, c1);
+    else code_pair_as<DT, BITS, RNG, false>(rawp, gc, nz, c0, c1);
 }
 // the eight codes of a group; the kind is decided once for the group (it is the same for the whole warp)
 template <int DT, int BITS, int RNG>
 __device__ __forceinline__ void codes8(const uint32_t (&raw)[4], const GroupConst<DT>& gc, const float2 (&nz)[4], uint32_t (&cb)[8]) {
     if (gc.special) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 2>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
-        return;
-    }
-    if constexpr (DT == GACT_F16 && NoOverflow<RNG>::value) {
-        if (gc.clamp) {
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, true>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+    } else {
 #pragma unroll
-            for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 1>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
-            return;
-        }
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, false>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
     }
-#pragma unroll
-    for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 0>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
 }
 // acc + (v << SHIFT) as a multiply-add: on the FMA pipe, which this kernel leaves idle, rather than the ALU
 __device__ __forceinline__ uint32_t shl_add(uint32_t v, int shift, uint32_t acc) {
@@ -304,79 +286,15 @@ __device__ __forceinline__ uint32_t shl_add(uint32_t v, int shift, uint32_t acc)
     return d;
 }
 
-// ---- one tile ---------------------------------------------------------------------------------------------------------
-// TG groups per tile (at least one row-block).  FULL: all of them exist and are complete.
+// The code pass of a tile: w0 / w1 are the words lanes L*k publish for group k (see GroupConst), smask the ballot of
+// special groups.
 template <int DT, int BITS, int RNG, int TG, bool FULL, class Src>
-__device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lane, const Src& src) {
+__device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, int lane, const Src& src, uint32_t w0, uint32_t w1,
+                                             unsigned smask) {
     constexpr int kTG = TG;
     constexpr int WPT = 8 / BITS, U = kTG / WPT;
-    constexpr int LPG = 32 / kTG;                           // lanes that end up with the same group's result
-    static_assert(U >= 1, "a tile holds whole row-blocks");
+    constexpr int LPG = 32 / kTG;
     const int64_t g0 = tile * kTG;
-    const int myk = lane / LPG;                             // the group whose min / max / scale this lane ends up with
-
-    // ---- pass 1: min, max, scale ----
-    uint32_t v[kTG];
-#pragma unroll
-    for (int k = 0; k < kTG; k++) {
-        uint32_t raw[4];
-        src.load(k, raw);
-        v[k] = lane_min_negmax<DT>(raw);
-    }
-    // the reference starts from +-1e30 in T, which is what remains of a group of NaNs
-    const uint32_t mnx = pmin2<DT>(tile_reduce<DT, kTG>(v, lane), start_pair<DT>());
-    float mn = pair_lo<DT>(mnx), mx = -pair_hi<DT>(mnx);
-    // a zero extreme takes the sign the reference's reduction order gives it (rare; decided per group by the whole warp)
-    const unsigned amb = __ballot_sync(kFull, zero_sign_ambiguous(mn, mx));
-    if (amb) {
-#pragma unroll
-        for (int k = 0; k < kTG; k++) {
-            if (amb & ((0xffffffffu >> (32 - LPG)) << (LPG * k))) {
-                uint32_t raw[4];
-                float vals[8];
-                src.load(k, raw);
-                raw_to_float<DT>(raw, vals);
-                const float z = zero_sign_like_reference<DT>(vals, lane);
-                if (myk == k) {
-                    if (mn == 0.0f) mn = z;
-                    if (mx == 0.0f) mx = z;
-                }
-            }
-        }
-    }
-    float sc;
-    uint32_t w0, w1;                                        // what pass 2 fetches from lane L*k
-    bool special, clampable = false;
-    if constexpr (DT == GACT_F16) {
-        sc = scale_f16<BITS>(mn, mx);
-        w0 = h2_bits(__float2half2_rn(mn));                 // both are half-precision values already
-        w1 = h2_bits(__float2half2_rn(sc));
-        special = (w1 & 0x7fffu) == 0x7c00u;
-        if constexpr (NoOverflow<RNG>::value) {
-            // No element's product can exceed the one of the group's range: t = round_h(x - mn) <= round_h(mx - mn), and
-            // rounding and the multiplication by a non-negative scale are monotone (NaN compares false).  A negative
-            // scale only comes out of a group of NaNs; it takes the clamped path too, with the sign removed.
-            const float range = Elem<GACT_F16>::round(__fsub_rn(mx, mn));
-            clampable = Elem<GACT_F16>::round(range * sc) > (float)((1 << BITS) - 1) || (int32_t)w1 < 0;
-        }
-    } else {
-        sc = compute_scale<DT>(mn, mx, BITS);
-        w0 = __float_as_uint(mn);
-        w1 = __float_as_uint(sc);
-        special = !(sc > 0.0f);
-    }
-    if ((lane & (LPG - 1)) == 0 && (FULL || g0 + myk < a.G)) {
-        if constexpr (DT == GACT_F16) {
-            ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 & 0xffffu);
-            ((unsigned short*)a.qscale)[g0 + myk] = (unsigned short)(w1 & 0xffffu);
-        } else {
-            ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 >> 16);
-            ((float*)a.qscale)[g0 + myk] = sc;
-        }
-    }
-    const unsigned smask = __ballot_sync(kFull, special), cmask = __ballot_sync(kFull, clampable);
-
-    // ---- pass 2: codes, one row-block at a time ----
     float2 nz_odd[4];            // FAST: noise of an odd group, produced together with the even group before it
 #pragma unroll
     for (int u = 0; u < U; u++) {
@@ -395,7 +313,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             for (int ni = 0; ni < WPT; ni++) {
                 const int k = u * WPT + ni;
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, LPG * k, smask, cmask);
+                gc.fetch(w0, w1, LPG * k, smask);
                 uint32_t raw[4];
                 src.load(k, raw);
                 const bool present = FULL || g0 + k < a.G;
@@ -405,13 +323,10 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
                     for (int i = 0; i < 4; i++) c[i] = 0x64006400u;
                 } else if (gc.special) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 2>(raw[i], gc.mn2, gc.sc2);
-                } else if (gc.clamp) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 1>(raw[i], gc.mn2, gc.scale_clean());
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, true>(raw[i], gc.mn2, gc.sc2);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 0>(raw[i], gc.mn2, gc.sc2);
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, false>(raw[i], gc.mn2, gc.sc2);
                 }
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc2[i] = shl_add(c[i], ni * BITS, acc2[i]);
@@ -425,7 +340,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             for (int j = 0; j < 8; j++) acc[j] = 0;
             GroupConst<DT> gc[WPT];
 #pragma unroll
-            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, LPG * (u * WPT + ni), smask, cmask);
+            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, LPG * (u * WPT + ni), smask);
             const uint64_t gid0 = (uint64_t)r * kGroup + lane * 8;
 #pragma unroll
             for (int c = 0; c < (WPT + 3) / 4; c++) {
@@ -478,7 +393,7 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
                     for (int i = 0; i < 4; i++) nz[i] = Centred<DT, RNG>::value ? add2(p[i], splat2(-0.5f)) : p[i];
                 }
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, LPG * k, smask, cmask);
+                gc.fetch(w0, w1, LPG * k, smask);
                 uint32_t raw[4];
                 src.load(k, raw);
                 uint32_t cb[8];
@@ -492,6 +407,78 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             st_stream_u2(dst, gather_bytes8(acc));
         }
     }
+}
+
+// ---- one tile ---------------------------------------------------------------------------------------------------------
+// TG groups per tile (at least one row-block).  FULL: all of them exist and are complete.
+template <int DT, int BITS, int RNG, int TG, bool FULL, class Src>
+__device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lane, const Src& src) {
+    constexpr int kTG = TG;
+    constexpr int WPT = 8 / BITS, U = kTG / WPT;
+    constexpr int LPG = 32 / kTG;                           // lanes that end up with the same group's result
+    static_assert(U >= 1, "a tile holds whole row-blocks");
+    const int64_t g0 = tile * kTG;
+    const int myk = lane / LPG;                             // the group whose min / max / scale this lane ends up with
+
+    // ---- pass 1: min, max, scale ----
+    uint32_t v[kTG];
+#pragma unroll
+    for (int k = 0; k < kTG; k++) {
+        uint32_t raw[4];
+        src.load(k, raw);
+        v[k] = lane_min_negmax<DT>(raw);
+    }
+    // the reference starts from +-1e30 in T, which is what remains of a group of NaNs
+    const uint32_t mnx = pmin2<DT>(tile_reduce<DT, kTG>(v, lane), start_pair<DT>());
+    float mn = pair_lo<DT>(mnx), mx = -pair_hi<DT>(mnx);
+    // a zero extreme takes the sign the reference's reduction order gives it (rare; decided per group by the whole warp)
+    const unsigned amb = __ballot_sync(kFull, zero_sign_ambiguous(mn, mx));
+    if (amb) {
+#pragma unroll
+        for (int k = 0; k < kTG; k++) {
+            if (amb & ((0xffffffffu >> (32 - LPG)) << (LPG * k))) {
+                uint32_t raw[4];
+                float vals[8];
+                src.load(k, raw);
+                raw_to_float<DT>(raw, vals);
+                const float z = zero_sign_like_reference<DT>(vals, lane);
+                if (myk == k) {
+                    if (mn == 0.0f) mn = z;
+                    if (mx == 0.0f) mx = z;
+                }
+            }
+        }
+    }
+    float sc;
+    uint32_t w0, w1;                                        // what pass 2 fetches from lane L*k
+    bool special;
+    if constexpr (DT == GACT_F16) {
+        sc = scale_f16<BITS>(mn, mx);
+        w0 = h2_bits(__float2half2_rn(mn));                 // both are half-precision values already
+        w1 = h2_bits(__float2half2_rn(sc));
+        special = (w1 & 0x7fffu) == 0x7c00u;
+    } else {
+        sc = compute_scale<DT>(mn, mx, BITS);
+        w0 = __float_as_uint(mn);
+        w1 = __float_as_uint(sc);
+        special = !(sc > 0.0f);
+    }
+    if ((lane & (LPG - 1)) == 0 && (FULL || g0 + myk < a.G)) {
+        if constexpr (DT == GACT_F16) {
+            ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 & 0xffffu);
+            ((unsigned short*)a.qscale)[g0 + myk] = (unsigned short)(w1 & 0xffffu);
+        } else {
+            ((unsigned short*)a.qmin)[g0 + myk] = (unsigned short)(w0 >> 16);
+            ((float*)a.qscale)[g0 + myk] = sc;
+        }
+    }
+    const unsigned smask = __ballot_sync(kFull, special);
+
+    // ---- pass 2: codes ----
+    // Almost every tile holds plain groups only; its code pass is compiled with the mask known to be zero, which
+    // removes every per-group test and branch from it.
+    if (smask == 0u) tile16_codes<DT, BITS, RNG, TG, FULL>(a, tile, lane, src, w0, w1, 0u);
+    else tile16_codes<DT, BITS, RNG, TG, FULL>(a, tile, lane, src, w0, w1, smask);
 }
 
 // ---- the warp-private bulk-copy ring -------------------------------------------------------------------------------
