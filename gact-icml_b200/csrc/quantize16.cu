@@ -16,19 +16,25 @@
 // are read straight from global memory, element by element where they must be.
 //
 // Tile routine.
-//   pass 1  two-wide min / max over the lane's four packed pairs, folded into one word (min, -max); the eight
-//           words of the tile are reduced across the warp together by a butterfly that halves the number of live
-//           words with every exchange (9 shuffles for 8 groups instead of 16 single-group reductions); lanes
-//           4k..4k+3 end up with group k's pair, compute its scale and write min / scale.
+//   pass 1  for the reduction a lane takes one contiguous 32nd of the tile (eight 16-byte chunks of ONE group,
+//           visited in a lane-dependent rotation to stay off bank conflicts), runs one two-wide min / max chain
+//           over them, folds the result into one word (min, -max) and finishes with two exchanges between the four
+//           lanes of the group; lanes 4k..4k+3 end up with group k's pair, compute its scale and write min / scale.
+//           The chain propagates NaN, which tells pass 2 whether a group holds one; a tile that does is reduced
+//           again with NaN ignored, as the reference does.  (Tiles read from global memory keep per-group chains
+//           and a butterfly over the eight words.)
 //           fp16 scale: the reference's double-precision quotient rounded to float and then to half is taken from
 //           an fp32 reciprocal whenever that cannot change the result (quotient further than 16 fp32 ulps from
 //           every half-precision rounding boundary, checked on the bit pattern); the double-precision path
 //           remains for the other ~0.4 % of the groups.
 //   pass 2  (x - min) * scale in two-wide half arithmetic with the reference's roundings (fp16), or one
 //           mixed-precision subtract and a packed fma in fp32 (bf16); noise added in fp32; w + 1.5*2^23 leaves
-//           rint(w) in the low mantissa bits (no conversion instruction); slots are summed with shifted adds and
+//           rint(w) in the low mantissa bits (no conversion instruction); slots are summed with multiply-adds and
 //           the bytes cut out with byte permutes.  fp16 round-to-nearest never leaves half precision: p + 1024
 //           rounds to the integer in the low mantissa bits of each half and two codes travel per instruction.
+//           Groups come in three kinds - plain, guarded (a NaN, an infinity, an overflowing range: the lower clamp
+//           matters), special (scale +inf / not positive); a tile of plain groups only, which is almost every
+//           tile, runs a copy of the pass compiled without any per-group test.
 #include <atomic>
 
 #include "quantize_common.cuh"
@@ -54,21 +60,26 @@ constexpr int kSmemBytes = kWarps * kStages * kTileBytesMax;   // 64 KB per bloc
 __device__ int g_pipeline_error = 0;
 
 // ---- two-wide helpers on the bit patterns of half2 / bfloat162 --------------------------------------------------
-template <int DT> __device__ __forceinline__ uint32_t pmin2(uint32_t a, uint32_t b) {
+// NP: NaN-propagating (a NaN operand gives NaN) instead of NaN-ignoring
+template <int DT, bool NP = false> __device__ __forceinline__ uint32_t pmin2(uint32_t a, uint32_t b) {
     if constexpr (DT == GACT_F16) {
-        const __half2 r = __hmin2(*(const __half2*)&a, *(const __half2*)&b);
+        const __half2 x = *(const __half2*)&a, y = *(const __half2*)&b;
+        const __half2 r = NP ? __hmin2_nan(x, y) : __hmin2(x, y);
         return *(const uint32_t*)&r;
     } else {
-        const __nv_bfloat162 r = __hmin2(*(const __nv_bfloat162*)&a, *(const __nv_bfloat162*)&b);
+        const __nv_bfloat162 x = *(const __nv_bfloat162*)&a, y = *(const __nv_bfloat162*)&b;
+        const __nv_bfloat162 r = NP ? __hmin2_nan(x, y) : __hmin2(x, y);
         return *(const uint32_t*)&r;
     }
 }
-template <int DT> __device__ __forceinline__ uint32_t pmax2(uint32_t a, uint32_t b) {
+template <int DT, bool NP = false> __device__ __forceinline__ uint32_t pmax2(uint32_t a, uint32_t b) {
     if constexpr (DT == GACT_F16) {
-        const __half2 r = __hmax2(*(const __half2*)&a, *(const __half2*)&b);
+        const __half2 x = *(const __half2*)&a, y = *(const __half2*)&b;
+        const __half2 r = NP ? __hmax2_nan(x, y) : __hmax2(x, y);
         return *(const uint32_t*)&r;
     } else {
-        const __nv_bfloat162 r = __hmax2(*(const __nv_bfloat162*)&a, *(const __nv_bfloat162*)&b);
+        const __nv_bfloat162 x = *(const __nv_bfloat162*)&a, y = *(const __nv_bfloat162*)&b;
+        const __nv_bfloat162 r = NP ? __hmax2_nan(x, y) : __hmax2(x, y);
         return *(const uint32_t*)&r;
     }
 }
@@ -85,19 +96,21 @@ template <int DT> __device__ __forceinline__ float pair_hi(uint32_t v) {
 // (hi, hi) with hi = the reference's start value 1e30 in T (half: +inf)
 template <int DT> __device__ __forceinline__ uint32_t start_pair() { return DT == GACT_F16 ? 0x7c007c00u : 0x714a714au; }
 
-// (min, -max) of the lane's 8 values; NaN values are ignored (an all-NaN lane yields NaN, ignored further on)
-template <int DT> __device__ __forceinline__ uint32_t lane_min_negmax(const uint32_t (&raw)[4]) {
-    const uint32_t lo = pmin2<DT>(pmin2<DT>(raw[0], raw[1]), pmin2<DT>(raw[2], raw[3]));
-    const uint32_t hi = pmax2<DT>(pmax2<DT>(raw[0], raw[1]), pmax2<DT>(raw[2], raw[3]));
+// (min, -max) of the lane's 8 values.  NP = false: NaN values are ignored (an all-NaN lane yields NaN, ignored
+// further on), which is the reference's min / max.  NP = true: any NaN makes both halves NaN - the same instruction
+// count, and the result doubles as the test for "this group holds a NaN".
+template <int DT, bool NP> __device__ __forceinline__ uint32_t lane_min_negmax(const uint32_t (&raw)[4]) {
+    const uint32_t lo = pmin2<DT, NP>(pmin2<DT, NP>(raw[0], raw[1]), pmin2<DT, NP>(raw[2], raw[3]));
+    const uint32_t hi = pmax2<DT, NP>(pmax2<DT, NP>(raw[0], raw[1]), pmax2<DT, NP>(raw[2], raw[3]));
     const uint32_t nh = hi ^ 0x80008000u;
-    return pmin2<DT>(__byte_perm(lo, nh, 0x5410u), __byte_perm(lo, nh, 0x7632u));
+    return pmin2<DT, NP>(__byte_perm(lo, nh, 0x5410u), __byte_perm(lo, nh, 0x7632u));
 }
 
 // Warp reduction of the tile's TG (min, -max) words at once.  The first log2(TG) exchanges (distance 16, 8, ...)
 // each halve the number of words a lane still carries (a lane keeps the groups whose index bit matches its lane bit
 // and hands the others over); the remaining distances finish the one word left.  With L = 32 / TG, lanes
 // L*k .. L*k + L-1 return group k's word.
-template <int DT, int TG> __device__ __forceinline__ uint32_t tile_reduce(uint32_t (&v)[TG], int lane) {
+template <int DT, int TG, bool NP> __device__ __forceinline__ uint32_t tile_reduce(uint32_t (&v)[TG], int lane) {
     static_assert(TG == 4 || TG == 8, "tile of 4 or 8 groups");
     int dist = 16;
 #pragma unroll
@@ -106,11 +119,11 @@ template <int DT, int TG> __device__ __forceinline__ uint32_t tile_reduce(uint32
 #pragma unroll
         for (int i = 0; i < half; i++) {
             const uint32_t keep = up ? v[i + half] : v[i], send = up ? v[i] : v[i + half];
-            v[i] = pmin2<DT>(keep, __shfl_xor_sync(kFull, send, dist));
+            v[i] = pmin2<DT, NP>(keep, __shfl_xor_sync(kFull, send, dist));
         }
     }
 #pragma unroll
-    for (; dist >= 1; dist >>= 1) v[0] = pmin2<DT>(v[0], __shfl_xor_sync(kFull, v[0], dist));
+    for (; dist >= 1; dist >>= 1) v[0] = pmin2<DT, NP>(v[0], __shfl_xor_sync(kFull, v[0], dist));
     return v[0];
 }
 
@@ -154,15 +167,57 @@ template <int DT> struct GlobalSrc {
     }
 };
 
+// (min, -max) of every group of the tile; lanes L*k .. L*k + L-1 return group k's word
+template <int DT, int TG, bool NP, class Src> __device__ __forceinline__ uint32_t tile_min_negmax(const Src& src, int lane) {
+    uint32_t v[TG];
+#pragma unroll
+    for (int k = 0; k < TG; k++) {
+        uint32_t raw[4];
+        src.load(k, raw);
+        v[k] = lane_min_negmax<DT, NP>(raw);
+    }
+    // the reference starts from +-1e30 in T, which is what remains of a group of NaNs
+    return pmin2<DT, NP>(tile_reduce<DT, TG, NP>(v, lane), start_pair<DT>());
+}
+
+// The same for a tile that lies in shared memory.  A reduction does not care which lane looks at which element, so
+// here a lane takes one contiguous 32nd of the tile - 8 (TG = 8) or 4 chunks of 16 bytes, all of ONE group - instead
+// of 16 bytes of every group: one long min / max chain per lane and L-1 exchanges between the L = 32 / TG lanes of a
+// group, 70 instructions per lane and tile of 8 groups instead of 112 for per-group chains, the fold of each and the
+// butterfly.  The chunks are visited in a lane-dependent rotation, which keeps the 16-byte reads of a quarter-warp
+// on different banks.
+template <int DT, int TG, bool NP> __device__ __forceinline__ uint32_t tile_min_negmax(const SmemSrc& src, int lane) {
+    constexpr int CH = TG * kGroup * 2 / 32 / 16, LPG = 32 / TG;
+    const unsigned char* mine = src.base + lane * ((CH - 1) * 16);          // base already holds lane * 16
+    const int rot = lane * CH / 8;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < CH; j++) {
+        const uint4 v = *(const uint4*)(mine + ((j + rot) & (CH - 1)) * 16);
+        const uint32_t a = pmin2<DT, NP>(pmin2<DT, NP>(v.x, v.y), pmin2<DT, NP>(v.z, v.w));
+        const uint32_t b = pmax2<DT, NP>(pmax2<DT, NP>(v.x, v.y), pmax2<DT, NP>(v.z, v.w));
+        lo = j == 0 ? a : pmin2<DT, NP>(lo, a);
+        hi = j == 0 ? b : pmax2<DT, NP>(hi, b);
+    }
+    const uint32_t nh = hi ^ 0x80008000u;
+    uint32_t v = pmin2<DT, NP>(__byte_perm(lo, nh, 0x5410u), __byte_perm(lo, nh, 0x7632u));
+#pragma unroll
+    for (int dist = 1; dist < LPG; dist <<= 1) v = pmin2<DT, NP>(v, __shfl_xor_sync(kFull, v, dist));
+    return pmin2<DT, NP>(v, start_pair<DT>());
+}
+
 // ---- codes of one pair of elements, as magic bits (1.5*2^23 + code) ------------------------------------------------
 // fp16: the reference's half-precision arithmetic, p = round_h(round_h(x - mn) * scale), max(p, 0) (NaN -> 0), no
 // upper clamp in the reference's modes (CURAND, EXTERNAL), clamp at 2^b - 1 in FAST / RTN.
-template <int BITS, int RNG>
+// GUARD = false: a group of finite values only, with a finite scale > 0.  There x - mn >= 0 (or +inf, by overflow),
+// the product is never NaN or negative, and max(p, 0) is the identity: it is left out.
+template <int BITS, int RNG, bool GUARD>
 __device__ __forceinline__ void code_pair_f16(uint32_t rawp, uint32_t mn2, uint32_t sc2, float2 nz, uint32_t& c0, uint32_t& c1) {
     constexpr float MAXC = (float)((1 << BITS) - 1);
     const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
     const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
-    __half2 p = __hmax2(__hmul2(t, as_h2(sc2)), zero2);
+    __half2 p = __hmul2(t, as_h2(sc2));
+    if (GUARD) p = __hmax2(p, zero2);
     if (NoOverflow<RNG>::value) p = __hmin2(p, maxc2);
     float2 r;
 #ifdef GACT_FAST_FLOOR
@@ -190,23 +245,26 @@ __device__ __forceinline__ void code_pair_f16_inf(uint32_t rawp, uint32_t mn2, u
     c1 = t.y > 0.0f ? top : 0u;
 }
 // fp16, round to nearest, staying in half precision: returns (0x6400 + code) in each half
-template <int BITS, bool INF_SCALE> __device__ __forceinline__ uint32_t code_pair_f16_rtn(uint32_t rawp, uint32_t mn2, uint32_t sc2) {
+// (KIND: 0 plain, 1 guarded, 2 scale +inf - see GroupConst)
+template <int BITS, int KIND> __device__ __forceinline__ uint32_t code_pair_f16_rtn(uint32_t rawp, uint32_t mn2, uint32_t sc2) {
     constexpr float MAXC = (float)((1 << BITS) - 1);
     const __half2 zero2 = __float2half2_rn(0.0f), maxc2 = __float2half2_rn(MAXC);
     const __half2 t = __hsub2(as_h2(rawp), as_h2(mn2));
     __half2 p;
-    if (INF_SCALE) p = __hmul2(__hgt2(t, zero2), maxc2);                                         // t > 0 ? 2^b - 1 : 0
-    else p = __hmin2(__hmax2(__hmul2(t, as_h2(sc2)), zero2), maxc2);
+    if (KIND == 2) p = __hmul2(__hgt2(t, zero2), maxc2);                                         // t > 0 ? 2^b - 1 : 0
+    else if (KIND == 1) p = __hmin2(__hmax2(__hmul2(t, as_h2(sc2)), zero2), maxc2);
+    else p = __hmin2(__hmul2(t, as_h2(sc2)), maxc2);
     return h2_bits(__hadd2(p, __float2half2_rn(1024.0f)));
 }
 // bf16 (our semantics): u = fma(x - mn, scale, noise - 0.5) in fp32, clamped to [0, 2^b - 1], NaN -> 0.
-// PLAIN: the group holds no infinity (scale > 0), so NaN can only come from a NaN element, and max(x, mn) - a
-// two-wide instruction that ignores NaN - sends those to the minimum, i.e. to code 0, like the clamp does; the
-// lower clamp is then implied (u >= -0.5 rounds to 0).
-template <int BITS, int RNG, bool PLAIN>
+// KIND 0: finite values only and scale > 0: u >= -0.5 and never NaN, both lower clamp and NaN rule are implied.
+// KIND 1: scale > 0 but the group holds a NaN: max(x, mn) - a two-wide instruction that ignores NaN - sends it to
+// the minimum, i.e. to code 0, like the clamp does.  KIND 2: anything else (an infinity in the group): clamped in fp32.
+template <int BITS, int RNG, int KIND>
 __device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, float nmn, float sc, float2 nz, uint32_t& c0, uint32_t& c1) {
     constexpr float MAXC = (float)((1 << BITS) - 1);
-    if (PLAIN) rawp = pmax2<GACT_BF16>(rawp, mn2);
+    constexpr bool PLAIN = KIND != 2;
+    if (KIND == 1) rawp = pmax2<GACT_BF16>(rawp, mn2);
     const float2 t = mixed_add2_bf16(rawp, splat2(nmn));
 #ifdef GACT_FAST_FLOOR
     if (RNG == GACT_RNG_FAST && PLAIN) {
@@ -225,58 +283,64 @@ __device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, floa
     c1 = __float_as_uint(r.y);
 }
 
-// what every lane needs to know about one group in pass 2
+// what every lane needs to know about one group in pass 2.  Kinds of group: 0 = plain (finite values only, a
+// finite scale > 0), 1 = guarded (it holds a NaN or, fp16, its scale is 0 or NaN because of an infinity or an
+// overflowing range: the reference's max(., 0) matters), 2 = special (fp16: scale +inf; bf16: not (scale > 0)).
+// Which groups are special / guarded travels as two ballot masks (bit L*k = group k): warp-uniform values.
 template <int DT> struct GroupConst;
 // fp16: lane L*k publishes min and scale, each already doubled into both halves of a word, so that pass 2 gets its
-// two-wide operands with two shuffles and no further instruction.  Which groups are special (scale +inf) travels as
-// a ballot mask (bit L*k = group k): a warp-uniform value.
+// two-wide operands with two shuffles and no further instruction.
 template <> struct GroupConst<GACT_F16> {
     uint32_t mn2, sc2;
-    bool special;                                   // scale is +inf
-    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask) {
+    int kind;
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask, unsigned gmask) {
         mn2 = __shfl_sync(kFull, w0, src);
         sc2 = __shfl_sync(kFull, w1, src);
-        special = (smask >> src) & 1u;
+        kind = ((smask >> src) & 1u) ? 2 : ((gmask >> src) & 1u) ? 1 : 0;
     }
 };
 template <> struct GroupConst<GACT_BF16> {
     uint32_t mn2;
     float nmn, sc;
-    bool special;                                   // not (scale > 0): the group holds an infinity, or only NaN
-    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask) {
+    int kind;
+    __device__ __forceinline__ void fetch(uint32_t w0, uint32_t w1, int src, unsigned smask, unsigned gmask) {
         const uint32_t m = __shfl_sync(kFull, w0, src);
         sc = __uint_as_float(__shfl_sync(kFull, w1, src));
         const __nv_bfloat162 hi = __high2bfloat162(*(const __nv_bfloat162*)&m);
         mn2 = *(const uint32_t*)&hi;
         nmn = -__uint_as_float(m);
-        special = (smask >> src) & 1u;
+        kind = ((smask >> src) & 1u) ? 2 : ((gmask >> src) & 1u) ? 1 : 0;
     }
 };
 
-template <int DT, int BITS, int RNG, bool SPECIAL>
+template <int DT, int BITS, int RNG, int KIND>
 __device__ __forceinline__ void code_pair_as(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
     if constexpr (DT == GACT_F16) {
-        if (SPECIAL) code_pair_f16_inf<BITS, RNG>(rawp, gc.mn2, c0, c1);
-        else code_pair_f16<BITS, RNG>(rawp, gc.mn2, gc.sc2, nz, c0, c1);
+        if (KIND == 2) code_pair_f16_inf<BITS, RNG>(rawp, gc.mn2, c0, c1);
+        else code_pair_f16<BITS, RNG, KIND == 1>(rawp, gc.mn2, gc.sc2, nz, c0, c1);
     } else {
-        code_pair_bf16<BITS, RNG, !SPECIAL>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
+        code_pair_bf16<BITS, RNG, KIND>(rawp, gc.mn2, gc.nmn, gc.sc, nz, c0, c1);
     }
 }
 // one pair, kind decided here (the reference-stream arrangement works pair by pair)
 template <int DT, int BITS, int RNG>
 __device__ __forceinline__ void code_pair(uint32_t rawp, const GroupConst<DT>& gc, float2 nz, uint32_t& c0, uint32_t& c1) {
-    if (gc.special) code_pair_as<DT, BITS, RNG, true>(rawp, gc, nz, c0, c1);
-    else code_pair_as<DT, BITS, RNG, false>(rawp, gc, nz, c0, c1);
+    if (gc.kind == 0) code_pair_as<DT, BITS, RNG, 0>(rawp, gc, nz, c0, c1);
+    else if (gc.kind == 1) code_pair_as<DT, BITS, RNG, 1>(rawp, gc, nz, c0, c1);
+    else code_pair_as<DT, BITS, RNG, 2>(rawp, gc, nz, c0, c1);
 }
 // the eight codes of a group; the kind is decided once for the group (it is the same for the whole warp)
 template <int DT, int BITS, int RNG>
 __device__ __forceinline__ void codes8(const uint32_t (&raw)[4], const GroupConst<DT>& gc, const float2 (&nz)[4], uint32_t (&cb)[8]) {
-    if (gc.special) {
+    if (gc.kind == 0) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, true>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 0>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+    } else if (gc.kind == 1) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 1>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, false>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
+        for (int i = 0; i < 4; i++) code_pair_as<DT, BITS, RNG, 2>(raw[i], gc, nz[i], cb[2 * i], cb[2 * i + 1]);
     }
 }
 // acc + (v << SHIFT) as a multiply-add: on the FMA pipe, which this kernel leaves idle, rather than the ALU
@@ -286,11 +350,11 @@ __device__ __forceinline__ uint32_t shl_add(uint32_t v, int shift, uint32_t acc)
     return d;
 }
 
-// The code pass of a tile: w0 / w1 are the words lanes L*k publish for group k (see GroupConst), smask the ballot of
-// special groups.
+// The code pass of a tile: w0 / w1 are the words lanes L*k publish for group k (see GroupConst), smask / gmask the
+// ballots of special and guarded groups.
 template <int DT, int BITS, int RNG, int TG, bool FULL, class Src>
 __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, int lane, const Src& src, uint32_t w0, uint32_t w1,
-                                             unsigned smask) {
+                                             unsigned smask, unsigned gmask) {
     constexpr int kTG = TG;
     constexpr int WPT = 8 / BITS, U = kTG / WPT;
     constexpr int LPG = 32 / kTG;
@@ -313,7 +377,7 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
             for (int ni = 0; ni < WPT; ni++) {
                 const int k = u * WPT + ni;
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, LPG * k, smask);
+                gc.fetch(w0, w1, LPG * k, smask, gmask);
                 uint32_t raw[4];
                 src.load(k, raw);
                 const bool present = FULL || g0 + k < a.G;
@@ -321,12 +385,15 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
                 if (!present) {
 #pragma unroll
                     for (int i = 0; i < 4; i++) c[i] = 0x64006400u;
-                } else if (gc.special) {
+                } else if (gc.kind == 0) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, true>(raw[i], gc.mn2, gc.sc2);
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 0>(raw[i], gc.mn2, gc.sc2);
+                } else if (gc.kind == 1) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 1>(raw[i], gc.mn2, gc.sc2);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, false>(raw[i], gc.mn2, gc.sc2);
+                    for (int i = 0; i < 4; i++) c[i] = code_pair_f16_rtn<BITS, 2>(raw[i], gc.mn2, gc.sc2);
                 }
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc2[i] = shl_add(c[i], ni * BITS, acc2[i]);
@@ -340,7 +407,7 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
             for (int j = 0; j < 8; j++) acc[j] = 0;
             GroupConst<DT> gc[WPT];
 #pragma unroll
-            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, LPG * (u * WPT + ni), smask);
+            for (int ni = 0; ni < WPT; ni++) gc[ni].fetch(w0, w1, LPG * (u * WPT + ni), smask, gmask);
             const uint64_t gid0 = (uint64_t)r * kGroup + lane * 8;
 #pragma unroll
             for (int c = 0; c < (WPT + 3) / 4; c++) {
@@ -393,7 +460,7 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
                     for (int i = 0; i < 4; i++) nz[i] = Centred<DT, RNG>::value ? add2(p[i], splat2(-0.5f)) : p[i];
                 }
                 GroupConst<DT> gc;
-                gc.fetch(w0, w1, LPG * k, smask);
+                gc.fetch(w0, w1, LPG * k, smask, gmask);
                 uint32_t raw[4];
                 src.load(k, raw);
                 uint32_t cb[8];
@@ -421,16 +488,16 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
     const int myk = lane / LPG;                             // the group whose min / max / scale this lane ends up with
 
     // ---- pass 1: min, max, scale ----
-    uint32_t v[kTG];
-#pragma unroll
-    for (int k = 0; k < kTG; k++) {
-        uint32_t raw[4];
-        src.load(k, raw);
-        v[k] = lane_min_negmax<DT>(raw);
-    }
-    // the reference starts from +-1e30 in T, which is what remains of a group of NaNs
-    const uint32_t mnx = pmin2<DT>(tile_reduce<DT, kTG>(v, lane), start_pair<DT>());
+    // First with NaN-propagating min / max: the result then also says whether the group holds a NaN (which the code
+    // pass wants to know).  The few tiles that do are reduced again the reference's way, NaN ignored.
+    uint32_t mnx = tile_min_negmax<DT, kTG, true>(src, lane);
     float mn = pair_lo<DT>(mnx), mx = -pair_hi<DT>(mnx);
+    const unsigned nanmask = __ballot_sync(kFull, mn != mn || mx != mx);
+    if (nanmask) {
+        mnx = tile_min_negmax<DT, kTG, false>(src, lane);
+        mn = pair_lo<DT>(mnx);
+        mx = -pair_hi<DT>(mnx);
+    }
     // a zero extreme takes the sign the reference's reduction order gives it (rare; decided per group by the whole warp)
     const unsigned amb = __ballot_sync(kFull, zero_sign_ambiguous(mn, mx));
     if (amb) {
@@ -451,12 +518,13 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
     }
     float sc;
     uint32_t w0, w1;                                        // what pass 2 fetches from lane L*k
-    bool special;
+    bool special, guard = (nanmask >> lane) & 1u;
     if constexpr (DT == GACT_F16) {
         sc = scale_f16<BITS>(mn, mx);
         w0 = h2_bits(__float2half2_rn(mn));                 // both are half-precision values already
         w1 = h2_bits(__float2half2_rn(sc));
         special = (w1 & 0x7fffu) == 0x7c00u;
+        guard = guard || !(sc > 0.0f);                      // scale 0 or NaN: an infinity in the group, or a range that overflows
     } else {
         sc = compute_scale<DT>(mn, mx, BITS);
         w0 = __float_as_uint(mn);
@@ -472,13 +540,13 @@ __device__ __forceinline__ void tile16(const QuantArgs& a, int64_t tile, int lan
             ((float*)a.qscale)[g0 + myk] = sc;
         }
     }
-    const unsigned smask = __ballot_sync(kFull, special);
+    const unsigned smask = __ballot_sync(kFull, special), gmask = __ballot_sync(kFull, guard);
 
     // ---- pass 2: codes ----
-    // Almost every tile holds plain groups only; its code pass is compiled with the mask known to be zero, which
+    // Almost every tile holds plain groups only; its code pass is compiled with both masks known to be zero, which
     // removes every per-group test and branch from it.
-    if (smask == 0u) tile16_codes<DT, BITS, RNG, TG, FULL>(a, tile, lane, src, w0, w1, 0u);
-    else tile16_codes<DT, BITS, RNG, TG, FULL>(a, tile, lane, src, w0, w1, smask);
+    if ((smask | gmask) == 0u) tile16_codes<DT, BITS, RNG, TG, FULL>(a, tile, lane, src, w0, w1, 0u, 0u);
+    else tile16_codes<DT, BITS, RNG, TG, FULL>(a, tile, lane, src, w0, w1, smask, gmask);
 }
 
 // ---- the warp-private bulk-copy ring -------------------------------------------------------------------------------
