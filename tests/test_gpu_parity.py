@@ -115,6 +115,51 @@ def test_fast_noise_arrangement(dtype, bits):
     check_case(make_input("relu", 256 * 5000 + 3, dtype, seed=3), bits, seed=2, rng_mode="fast")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bits", BITS)
+def test_kinds_of_group_side_by_side(dtype, bits):
+    """The 16-bit kernel treats three kinds of group differently (plain; guarded: a NaN, an infinity or an
+    overflowing range; special: scale +inf or not positive) and runs tiles of plain groups through a copy of the code
+    pass without per-group tests.  Here every kind sits next to every other, tile by tile (tiles of 4 and 8 groups)."""
+    g = torch.Generator().manual_seed(17)
+
+    def group(kind):
+        x = torch.randn(256, generator=g)
+        if kind == 1:
+            x[7] = float("nan")
+        elif kind == 2:
+            x[:] = float("nan")
+        elif kind == 3:
+            x[200] = float("inf")
+        elif kind == 4:
+            x[31] = float("-inf")
+        elif kind == 5:
+            x[0], x[255] = 60000.0, -60000.0           # the range overflows half precision
+        elif kind == 6:
+            x[:] = 1.25                                # fp16: scale +inf
+        elif kind == 7:
+            x = 1.0 + x * 1e-7                         # a range of a few ulps, or none
+        elif kind == 8:
+            x[3], x[4], x[100] = float("nan"), float("inf"), float("-inf")
+        elif kind == 9:
+            x = x.clamp_min(0)
+        elif kind == 10:
+            x[::2] = float("nan")
+        return x
+
+    order = [0] * 8 + list(range(11)) + [0] * 5 + [1, 0, 0, 0, 0, 0, 0, 0] + [0, 0, 0, 0, 6, 0, 0, 0] + [9] * 8 \
+        + [5, 0, 0, 3] + [0] * 12 + [2, 2, 2, 2, 2, 2, 2, 2] + [10, 7, 4, 8, 0, 9, 6, 5]
+    x = torch.cat([group(k) for k in order] + [torch.randn(100, generator=g)]).to(dtype)
+    for mode in ("fast", "curand", "rtn"):
+        check_case(x, bits, seed=5, rng_mode=mode)
+    # the same groups in a tensor large enough for tiles of 8 groups (two rounds over the resident warps)
+    if dtype != torch.float32 and bits in (2, 8):
+        big = make_input("relu", 256 * 60000, dtype, seed=8)
+        big[256 * 1000:256 * 1000 + x.numel()] = x
+        big[256 * 59990:256 * 59990 + 256 * 8] = x[256 * 8:256 * 16]
+        check_case(big, bits, seed=6, rng_mode="fast")
+
+
 @pytest.mark.parametrize("bits", BITS)
 def test_fp32_unfused_multiply_add(bits):
     x = make_input("randn", 256 * 40 + 3, torch.float32, seed=8)
