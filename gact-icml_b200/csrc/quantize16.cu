@@ -366,7 +366,44 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
         if (!FULL && r >= a.R) break;
         uint8_t* dst = a.packed + r * kGroup + lane * 8;
 
-        if constexpr (DT == GACT_F16 && RNG == GACT_RNG_RTN) {
+        if constexpr (DT == GACT_F16 && RNG == GACT_RNG_FAST && BITS == 1) {
+            // One-bit codes never leave half precision either.  code = rint(clamp(p, 0, 1) + noise - 0.5) is 1 exactly
+            // when p > 1 - noise =: thr (p + noise - 0.5 is exact in fp32, a tie at 0.5 rounds to the even 0, and
+            // neither clamp nor a NaN - for which the comparison is false, like NaN -> 0 - changes the outcome).
+            // thr = (255.5 - b) / 256 comes exact out of one two-wide fma on the halves 1024 + (255 - b), which a
+            // byte permute builds from the inverted noise word; the bits are summed into 1024 + byte by a second one.
+            const __half2 c2m8 = __float2half2_rn(0.00390625f), off = __float2half2_rn(-3.998046875f), zero2 = __float2half2_rn(0.0f);
+            uint32_t acc2[4] = {0x64006400u, 0x64006400u, 0x64006400u, 0x64006400u};
+            uint32_t nb[4];                                 // inverted noise bytes of an even group and the odd one after it
+#pragma unroll
+            for (int ni = 0; ni < WPT; ni++) {
+                const int k = u * WPT + ni;
+                if (!FULL && g0 + k >= a.G) break;
+                if ((k & 1) == 0) {
+                    fast_bytes16((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nb);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) nb[i] = ~nb[i];
+                }
+                GroupConst<DT> gc;
+                gc.fetch(w0, w1, LPG * k, smask, gmask);
+                uint32_t raw[4];
+                src.load(k, raw);
+                const __half2 weight = __float2half2_rn((float)(1 << ni));
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const __half2 t = __hsub2(as_h2(raw[i]), as_h2(gc.mn2));
+                    __half2 bit;
+                    if (gc.kind == 2) {
+                        bit = __hgt2(t, zero2);             // scale +inf: every element above the minimum gets the top code
+                    } else {
+                        const uint32_t hb = __byte_perm(nb[2 * (k & 1) + (i >> 1)], 0x64646464u, (i & 1) ? 0x4342u : 0x4140u);
+                        bit = __hgt2(__hmul2(t, as_h2(gc.sc2)), __hfma2(as_h2(hb), c2m8, off));
+                    }
+                    acc2[i] = h2_bits(__hfma2(bit, weight, as_h2(acc2[i])));
+                }
+            }
+            st_stream_u2(dst, make_uint2(__byte_perm(acc2[0], acc2[1], 0x6420u), __byte_perm(acc2[2], acc2[3], 0x6420u)));
+        } else if constexpr (DT == GACT_F16 && RNG == GACT_RNG_RTN) {
             // two codes per register: every slot adds (0x6400 + code) << shift; the 0x6400s are taken out again by the
             // start value, and what they carry across the halves cancels with it (arithmetic modulo 2^32)
             uint32_t init = 0;

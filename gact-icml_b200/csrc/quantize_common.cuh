@@ -45,10 +45,15 @@ template <int RNG> struct NoOverflow { static constexpr bool value = (RNG == GAC
 #ifndef GACT_FAST_ROUNDS
 #define GACT_FAST_ROUNDS 7
 #endif
+// the 16 noise bytes themselves: words 0, 1 = the even group's elements 0..3, 4..7; words 2, 3 = the odd group's
+__device__ __forceinline__ void fast_bytes16(uint64_t block, const PhiloxKeys& rk, uint32_t (&w)[4]) {
+    const uint4 r = philox4x32<GACT_FAST_ROUNDS>((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
+    w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+}
 template <bool CENTRED>
 __device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& rk, float2 (&even)[4], float2 (&odd)[4]) {
-    const uint4 r = philox4x32<GACT_FAST_ROUNDS>((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    uint32_t w[4];
+    fast_bytes16(block, rk, w);
     // byte -> float without a conversion: a byte permute drops it into bits 8..15 of the mantissa of 2^23, giving
     // 2^23 + 256*b; times 2^-16 that is 128 + b/256, and the offset below brings (b + 0.5)/256 (- 0.5), all exact
     const float2 s2 = splat2(1.52587890625e-05f), o2 = splat2((CENTRED ? -0.498046875f : 0.001953125f) - 128.0f);
