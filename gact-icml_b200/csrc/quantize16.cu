@@ -641,7 +641,7 @@ __global__ void __launch_bounds__(kThreads16, GACT_Q16_MINB) quantize16_kernel(c
         int64_t i = 0;
         for (int64_t t = gw; t < bulk_tiles; t += nw, ++i) {
             const int s = (int)(i % kStages);
-            // all lanes poll; the verdict is taken jointly so that the warp never splits
+            // all lanes poll; the outcome is decided jointly so that the warp never splits
             if (!__all_sync(kFull, mbar_wait(bar0 + 8 * s, (uint32_t)((i / kStages) & 1), a.wait_limit))) {
                 if (lane == 0) atomicExch(&g_pipeline_error, 2);
                 // do not leave while copies into the other stages may still be in flight
