@@ -160,6 +160,30 @@ def test_kinds_of_group_side_by_side(dtype, bits):
         check_case(big, bits, seed=6, rng_mode="fast")
 
 
+def test_random_cases_soak():
+    """Sixty seeded random cases - dtype, width, noise mode, size (1 .. 3 M elements), distribution, storage offset -
+    each compared bit for bit with the oracle."""
+    import random
+    rnd = random.Random(20240607)
+    kinds = ["randn", "relu", "uniform", "tiny", "large", "special", "zeros_signed"]
+    for case in range(60):
+        dtype = rnd.choice(DTYPES)
+        bits = rnd.choice(BITS)
+        mode = rnd.choice(["fast", "fast", "curand", "rtn"])
+        n = rnd.choice([rnd.randint(1, 5000), rnd.randint(5000, 300000), rnd.randint(300000, 3000000)])
+        off = rnd.choice([0, 0, 1, 3, 8])
+        x = make_input(rnd.choice(kinds), n + off, dtype, seed=case)
+        xg = x.cuda()[off:]
+        seed = rnd.getrandbits(40)
+        pk, mn, sc = abi_quantize(xg, bits, seed, mode)
+        opk, omn, osc = oracle.quantize(x[off:].contiguous(), bits, seed, mode)
+        tag = f"case {case}: {dtype} b={bits} n={n} off={off} {mode}"
+        assert_bits_equal(mn, omn, "qmin " + tag)
+        assert_bits_equal(sc, osc, "qscale " + tag)
+        assert_bits_equal(pk, opk, "packed " + tag)
+        assert_bits_equal(abi_dequantize(pk, mn, sc, n, bits), oracle.dequantize(opk, omn, osc, n, bits), "dequantized " + tag)
+
+
 @pytest.mark.parametrize("bits", BITS)
 def test_fp32_unfused_multiply_add(bits):
     x = make_input("randn", 256 * 40 + 3, torch.float32, seed=8)
