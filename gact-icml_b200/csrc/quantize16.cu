@@ -220,14 +220,6 @@ __device__ __forceinline__ void code_pair_f16(uint32_t rawp, uint32_t mn2, uint3
     if (GUARD) p = __hmax2(p, zero2);
     if (NoOverflow<RNG>::value) p = __hmin2(p, maxc2);
     float2 r;
-#ifdef GACT_FAST_FLOOR
-    if (RNG == GACT_RNG_FAST) {
-        r = fma2_rm(mixed_fma2_256(p, nz), splat2(0.00390625f), splat2(kMagic - 128.0f));
-        c0 = __float_as_uint(r.x);
-        c1 = __float_as_uint(r.y);
-        return;
-    }
-#endif
     if (RNG == GACT_RNG_RTN) r = add2(__half22float2(p), splat2(kMagic));                        // (p + 0.5) - 0.5 = p
     else if (Centred<GACT_F16, RNG>::value) r = add2(mixed_add2(p, nz), splat2(kMagic));         // p + (noise - 0.5)
     else r = add2(add2(mixed_add2(p, nz), splat2(-0.5f)), splat2(kMagic));                       // u - 0.5 >= -0.5 rounds to 0
@@ -266,15 +258,6 @@ __device__ __forceinline__ void code_pair_bf16(uint32_t rawp, uint32_t mn2, floa
     constexpr bool PLAIN = KIND != 2;
     if (KIND == 1) rawp = pmax2<GACT_BF16>(rawp, mn2);
     const float2 t = mixed_add2_bf16(rawp, splat2(nmn));
-#ifdef GACT_FAST_FLOOR
-    if (RNG == GACT_RNG_FAST && PLAIN) {
-        const float2 wp = fma2(t, splat2(sc * 65536.0f), nz);
-        const float2 rr = fma2_rm(wp, splat2(1.52587890625e-05f), splat2(kMagic - 128.0f));
-        c0 = __float_as_uint(rr.x);
-        c1 = __float_as_uint(rr.y);
-        return;
-    }
-#endif
     float2 w = fma2(t, splat2(sc), nz);
     if (!PLAIN) { w.x = fmaxf(w.x, 0.0f); w.y = fmaxf(w.y, 0.0f); }
     if (!NoOverflow<RNG>::value) { w.x = fminf(w.x, MAXC); w.y = fminf(w.y, MAXC); }
@@ -359,6 +342,8 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
     constexpr int WPT = 8 / BITS, U = kTG / WPT;
     constexpr int LPG = 32 / kTG;
     const int64_t g0 = tile * kTG;
+    // FAST: Philox counter of this lane for the tile's first pair of groups (g0 is even); a pair further on adds 32
+    const uint64_t blk0 = (uint64_t)(g0 >> 1) * (kGroup / 8) + lane;
     float2 nz_odd[4];            // FAST: noise of an odd group, produced together with the even group before it
 #pragma unroll
     for (int u = 0; u < U; u++) {
@@ -380,7 +365,7 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
                 const int k = u * WPT + ni;
                 if (!FULL && g0 + k >= a.G) break;
                 if ((k & 1) == 0) {
-                    fast_bytes16((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nb);
+                    fast_bytes16(blk0 + (uint64_t)(k >> 1) * (kGroup / 8), a.rk, nb);
 #pragma unroll
                     for (int i = 0; i < 4; i++) nb[i] = ~nb[i];
                 }
@@ -479,11 +464,7 @@ __device__ __forceinline__ void tile16_codes(const QuantArgs& a, int64_t tile, i
                 float2 nz[4];
                 if (RNG == GACT_RNG_FAST) {
                     if ((k & 1) == 0) {
-#ifdef GACT_FAST_FLOOR
-                        fast_raw16<(DT == GACT_F16 ? 0x47000080u : 0x4B000080u)>((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
-#else
-                        fast_noise16<true>((uint64_t)((g0 + k) >> 1) * (kGroup / 8) + lane, a.rk, nz, nz_odd);
-#endif
+                        fast_noise16<true>(blk0 + (uint64_t)(k >> 1) * (kGroup / 8), a.rk, nz, nz_odd);
                     } else {
 #pragma unroll
                         for (int i = 0; i < 4; i++) nz[i] = nz_odd[i];

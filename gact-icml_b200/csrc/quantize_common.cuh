@@ -67,35 +67,6 @@ __device__ __forceinline__ void fast_noise16(uint64_t block, const PhiloxKeys& r
     }
 }
 
-#ifdef GACT_FAST_FLOOR
-// EXPERIMENT (timing only): the same 16 noise bytes as float bit patterns K + b * 2^s + 2^(s-1), with the constant
-// and the half-unit offset coming out of the byte permute: no scaling instruction.
-template <uint32_t K>
-__device__ __forceinline__ void fast_raw16(uint64_t block, const PhiloxKeys& rk, float2 (&even)[4], float2 (&odd)[4]) {
-    const uint4 r = philox4x32<GACT_FAST_ROUNDS>((uint32_t)block, (uint32_t)(block >> 32), 0u, 0x46415354u, rk);
-    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        float2 (&dst)[4] = (i < 2) ? even : odd;
-        dst[(2 * i) & 3] = make_float2(__uint_as_float(__byte_perm(w[i], K, 0x7604u)), __uint_as_float(__byte_perm(w[i], K, 0x7614u)));
-        dst[(2 * i + 1) & 3] = make_float2(__uint_as_float(__byte_perm(w[i], K, 0x7624u)), __uint_as_float(__byte_perm(w[i], K, 0x7634u)));
-    }
-}
-__device__ __forceinline__ float2 fma2_rm(float2 a, float2 b, float2 c) {
-    float2 d;
-    asm("{ .reg .b64 ra, rb, rc, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; mov.b64 rc, {%6,%7}; fma.rm.f32x2 rd, ra, rb, rc; "
-        "mov.b64 {%0,%1}, rd; }"
-        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-    return d;
-}
-// float(h) * 256 + c for both halves (mixed-precision fma)
-__device__ __forceinline__ float2 mixed_fma2_256(__half2 h, float2 c) {
-    float2 d;
-    asm("{ .reg .b16 lo, hi, m; mov.b32 {lo, hi}, %2; mov.b16 m, 0x5c00; fma.rn.f32.f16 %0, lo, m, %3; fma.rn.f32.f16 %1, hi, m, %4; }"
-        : "=f"(d.x), "=f"(d.y) : "r"(*(const uint32_t*)&h), "f"(c.x), "f"(c.y));
-    return d;
-}
-#endif
 
 // cuRAND's uniform of two words: float(word) * 2^-32 + 2^-33 (minus 0.5 when CENTRED)
 template <bool CENTRED>
