@@ -349,7 +349,10 @@ PyObject* hooks_dequantize(PyObject*, PyObject* const* args, Py_ssize_t nargs) {
     } else {
         if (!PyTuple_Check(strides_o.p) || (size_t)PyTuple_GET_SIZE(strides_o.p) != dims.size()) return not_mine();
         std::vector<int64_t> str(dims.size());
-        for (size_t i = 0; i < dims.size(); i++) str[i] = PyLong_AsLongLong(PyTuple_GET_ITEM(strides_o.p, (Py_ssize_t)i));
+        for (size_t i = 0; i < dims.size(); i++) {
+            str[i] = PyLong_AsLongLong(PyTuple_GET_ITEM(strides_o.p, (Py_ssize_t)i));
+            if (str[i] == -1 && PyErr_Occurred()) return nullptr;
+        }
         out = at::empty_strided(dims, str, opts);
     }
     unsigned char* base = (unsigned char*)buf.data_ptr();
@@ -377,9 +380,9 @@ PyObject* hooks_dequantize(PyObject*, PyObject* const* args, Py_ssize_t nargs) {
 PyObject* hooks_launches(PyObject*, PyObject*) { return PyLong_FromLongLong(g_launches); }
 
 PyObject* hooks_bind(PyObject*, PyObject* packed_type) {
+    Py_INCREF(packed_type);
     Py_XDECREF(g_packed_type);
     g_packed_type = packed_type;
-    Py_INCREF(g_packed_type);
     Py_RETURN_NONE;
 }
 
