@@ -37,7 +37,7 @@ long long g_launches = 0;          // library kernels enqueued from here (benchm
 #define GACT_NAMES(X)                                                                                                         \
     X(unrelated_tensors) X(tid) X(iter) X(tids_registered) X(bits) X(seeds) X(dims) X(default_bit) X(seed_iter) X(seed_offset)    \
     X(swap) X(ptr_qtensor_map) X(layer_key_map) X(_live) X(check_dup) X(dedup_saved) X(keep_layout) X(rng_mode) X(fma)           \
-    X(quantize_bf16) X(shape) X(dtype) X(buf) X(n) X(strides)
+    X(quantize_bf16) X(shape) X(dtype) X(buf) X(n) X(strides) X(pack_bool_masks)
 #define X(name) PyObject* s_##name = nullptr;
 GACT_NAMES(X)
 #undef X
@@ -121,6 +121,66 @@ PyObject* status_error(int st, const char* what) {
     return nullptr;
 }
 
+// 1 = the tensor's address is listed in quantizer.unrelated_tensors (parameters), 0 = not, -1 = error
+int is_unrelated(PyObject* self, const at::Tensor& t) {
+    Ref unrelated(attr(self, s_unrelated_tensors));
+    Ref ptr(PyLong_FromUnsignedLongLong((unsigned long long)(uintptr_t)t.data_ptr()));
+    if (!unrelated || !ptr) return -1;
+    return PySequence_Contains(unrelated.p, ptr.p);
+}
+
+// torch.bool dropout masks: the decisions of Quantizer.check_quantize and the payload of Quantizer._quantize_mask,
+// (True, True, [words, shape, torch.bool]).  No quantizer state is involved.
+PyObject* quantize_bool_mask(PyObject* self, PyObject* config, PyObject* input, const at::Tensor& t) {
+    bool on = false;
+    if (!truthy_attr(config, s_pack_bool_masks, on)) return nullptr;
+    if (!on || t.layout() != at::kStrided || t.numel() == 0 || !t.is_cuda()) return PyTuple_Pack(2, Py_False, input);
+    const int hit = is_unrelated(self, t);
+    if (hit < 0) return nullptr;
+    if (hit) return PyTuple_Pack(2, Py_False, input);
+    const at::Tensor x = t.contiguous();
+    const int64_t n = x.numel();
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor words = at::empty({gact_mask_words(n)}, at::TensorOptions().dtype(at::kInt).device(x.device()));
+    void* stream = (void*)c10::cuda::getCurrentCUDAStream(x.device().index()).stream();
+    const int rc = gact_mask_pack((const uint8_t*)x.data_ptr(), n, (uint32_t*)words.data_ptr(), nullptr, stream);
+    g_launches++;
+    if (rc) return status_error(rc, "gact_mask_pack");
+    Ref words_o(THPVariable_Wrap(words)), shape(attr(input, s_shape)), dtype_o(attr(input, s_dtype));
+    if (!words_o || !shape || !dtype_o) return nullptr;
+    Ref payload(PyList_New(3));
+    if (!payload) return nullptr;
+    PyList_SET_ITEM(payload.p, 0, words_o.release());
+    PyList_SET_ITEM(payload.p, 1, shape.release());
+    PyList_SET_ITEM(payload.p, 2, dtype_o.release());
+    return PyTuple_Pack(3, Py_True, Py_True, payload.p);
+}
+
+// the inverse, for payloads of the form [int32 words, shape, torch.bool]; NotImplemented for anything else
+PyObject* dequantize_bool_mask(PyObject* payload) {
+    if (!PyList_Check(payload) || PyList_GET_SIZE(payload) != 3) return not_mine();
+    PyObject *words_o = PyList_GET_ITEM(payload, 0), *shape = PyList_GET_ITEM(payload, 1), *dtype_o = PyList_GET_ITEM(payload, 2);
+    if (!THPVariable_Check(words_o) || !PyTuple_Check(shape) || !THPDtype_Check(dtype_o) || ((THPDtype*)dtype_o)->scalar_type != at::kBool)
+        return not_mine();
+    const at::Tensor& words = THPVariable_Unpack(words_o);
+    if (!words.is_cuda() || words.scalar_type() != at::kInt || !words.is_contiguous()) return not_mine();
+    std::vector<int64_t> dims((size_t)PyTuple_GET_SIZE(shape));
+    int64_t n = 1;
+    for (size_t i = 0; i < dims.size(); i++) {
+        dims[i] = PyLong_AsLongLong(PyTuple_GET_ITEM(shape, (Py_ssize_t)i));
+        if (dims[i] == -1 && PyErr_Occurred()) return nullptr;
+        n *= dims[i];
+    }
+    if (words.numel() < gact_mask_words(n)) return not_mine();            // the Python path words the error
+    c10::cuda::CUDAGuard guard(words.device());
+    at::Tensor out = at::empty(dims, at::TensorOptions().dtype(at::kBool).device(words.device()));
+    void* stream = (void*)c10::cuda::getCurrentCUDAStream(words.device().index()).stream();
+    const int rc = gact_mask_unpack((const uint32_t*)words.data_ptr(), n, (uint8_t*)out.data_ptr(), stream);
+    g_launches++;
+    if (rc) return status_error(rc, "gact_mask_unpack");
+    return THPVariable_Wrap(out);
+}
+
 // quantize(quantizer, config, tensor) -> the tuple autograd keeps, or NotImplemented
 PyObject* hooks_quantize(PyObject*, PyObject* const* args, Py_ssize_t nargs) {
     HANDLE_TH_ERRORS
@@ -133,8 +193,10 @@ PyObject* hooks_quantize(PyObject*, PyObject* const* args, Py_ssize_t nargs) {
         bool bf16_on = false;
         if (!truthy_attr(config, s_quantize_bf16, bf16_on)) return nullptr;
         if (!bf16_on) return not_mine();
+    } else if (st == at::kBool) {
+        return quantize_bool_mask(self, config, input, t);
     } else if (st != at::kFloat && st != at::kHalf) {
-        return not_mine();                       // masks and everything else: the Python filter decides
+        return not_mine();                       // uint8 masks and everything else: the Python filter decides
     }
     bool swap = false, check_dup = false, dedup = false;
     if (!truthy_attr(self, s_swap, swap) || !truthy_attr(config, s_check_dup, check_dup) || !truthy_attr(config, s_dedup_saved, dedup)) return nullptr;
@@ -311,7 +373,8 @@ PyObject* hooks_dequantize(PyObject*, PyObject* const* args, Py_ssize_t nargs) {
         Py_INCREF(r);
         return r;
     }
-    if (PyTuple_GET_SIZE(saved) != 5 || PyTuple_GET_ITEM(saved, 1) != Py_False) return not_mine();   // dropout mask
+    if (PyTuple_GET_SIZE(saved) == 3 && PyTuple_GET_ITEM(saved, 1) == Py_True) return dequantize_bool_mask(PyTuple_GET_ITEM(saved, 2));
+    if (PyTuple_GET_SIZE(saved) != 5 || PyTuple_GET_ITEM(saved, 1) != Py_False) return not_mine();
     bool swap = false;
     if (!truthy_attr(self, s_swap, swap)) return nullptr;
     if (swap) return not_mine();

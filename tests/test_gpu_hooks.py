@@ -75,12 +75,61 @@ def test_same_tuples_state_and_bytes(dtype):
         assert a.stride() == b.stride() and a.dtype == b.dtype and torch.equal(a, b), name
 
 
+def test_bool_masks_native_and_python_agree():
+    """torch.bool dropout masks take the native path too; payload, tuple format and restored mask equal the Python
+    path's, the quantizer's state is untouched, and the decisions of the filter are the same."""
+    import gact
+    from gact import ops
+    from gact.quantizer import Quantizer
+    gact.config.reset()
+    q = Quantizer(4, False, False)
+
+    def both(fn):                                   # the same call on the native and on the Python path
+        gact.config.native_hooks = True
+        a = fn()
+        gact.config.native_hooks = False
+        b = fn()
+        gact.config.native_hooks = True
+        return a, b
+
+    for shape in ((100, 77), (64, 16, 128, 128), (5,), (3, 512)):
+        m = torch.rand(*shape, device="cuda") < 0.3
+        before = ops._hooks.launches()
+        rn, rp = both(lambda: q.quantize(m))
+        assert ops._hooks.launches() == before + 1
+        assert rn[0] is True and rn[1] is True and rp[0] is True and rp[1] is True and len(rn) == len(rp) == 3
+        assert torch.equal(rn[2][0], rp[2][0]) and rn[2][0].dtype == torch.int32
+        assert tuple(rn[2][1]) == tuple(rp[2][1]) == shape and rn[2][2] is torch.bool and rp[2][2] is torch.bool
+        assert q.tid == 0 and not q.ptr_qtensor_map
+        for r in (rn, rp):                          # payloads are interchangeable
+            on, op_ = both(lambda: q.dequantize(r))
+            assert on.dtype == torch.bool and torch.equal(on, m) and torch.equal(op_, m)
+        assert ops._hooks.launches() == before + 3
+    # a transposed mask is packed in its logical order, like the Python path does
+    m = (torch.rand(40, 600, device="cuda") < 0.5).t()
+    rn, rp = both(lambda: q.quantize(m))
+    assert torch.equal(rn[2][0], rp[2][0]) and torch.equal(q.dequantize(rn), m)
+    # the filter: empty, CPU and unrelated masks pass through; pack_bool_masks off leaves masks alone
+    for t in (torch.zeros(0, 4, dtype=torch.bool, device="cuda"), torch.ones(4, 4, dtype=torch.bool)):
+        for r in both(lambda: q.quantize(t)):
+            assert r[0] is False and r[1] is t
+    m = torch.rand(64, 64, device="cuda") < 0.5
+    q.unrelated_tensors.add(m.data_ptr())
+    assert all(r[0] is False for r in both(lambda: q.quantize(m)))
+    gact.config.pack_bool_masks = False
+    try:
+        m2 = torch.rand(64, 64, device="cuda") < 0.5
+        assert all(r[0] is False for r in both(lambda: q.quantize(m2)))
+    finally:
+        gact.config.reset()
+
+
 def test_cases_left_to_the_python_path():
-    """Masks, 32-bit passthrough, swapping and value fingerprints are handed back untouched."""
+    """uint8 masks, 32-bit passthrough, swapping and value fingerprints are handed back untouched."""
     import gact
     from gact import ops
     q = _quantizer(True)
-    m = torch.rand(100, 77, device="cuda") < 0.5
+    m = (torch.rand(100, 77, device="cuda") < 0.5).to(torch.uint8)
     before = ops._hooks.launches()
     r = q.quantize(m)
     assert r[0] and r[1] and torch.equal(q.dequantize(r), m) and ops._hooks.launches() == before
